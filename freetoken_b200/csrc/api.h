@@ -14,6 +14,7 @@
 #define FTK_GATE_SILU 1
 // the bias belongs to the logit: choice by logit + bias, weights = softmax of logit + bias over the chosen experts
 #define FTK_SCORE_SOFTMAX_OF_CHOSEN 2
+#define FTK_SCORE_SIGMOID_RAW 3  // sigmoid scores, the chosen experts' scores as weights without renormalising
 
 #ifdef __cplusplus
 extern "C" {
@@ -75,6 +76,8 @@ typedef struct {
   // Of the tcgen05 kernels the one with 128-row tiles takes it; not with block selection.
   int has_sink;
   float sink_logit;
+  // with has_sink: one logit per query head [n_q_heads] (float32) instead of sink_logit; null = sink_logit for all
+  const float* sink_heads;
 } FtkAttnExtras;
 
 const char* ftk_last_error(void);
@@ -127,6 +130,45 @@ int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_s
                  const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, int any_single, int any_multi,
                  float* carry, float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
                  void* stream);
+// Short causal convolution over time with a residual (shortconv.cu): out[t, c] = x[t, c] + sum_j w[c, j] *
+// in(t - taps + 1 + j, c) over the request's own inputs; the last taps - 1 inputs of every request live in its
+// state slot (state [n_slots, taps - 1, channels] float32, oldest first; zeros before the sequence's start) and are
+// replaced by this call.  x float32 (the stream), out of `dtype`.
+int ftk_short_conv(const float* x, const float* w, int taps, float* state, int n_slots, const int32_t* state_slots,
+                   const int32_t* seg_info, int n_segs, void* out, int dtype, int n_tokens, int channels, void* stream);
+// hist[n_prev] = x; x = sum_{j <= n_prev} mix[j] * hist[j] (rows of n floats, layer_stride apart; all float32).
+int ftk_depth_mix(float* hist, long long layer_stride, int n_prev, const float* mix, float* x, long long n, void* stream);
+// out[r, :] = weights[sorted_routes[r]] * h[sorted_routes[r] / top_k, :]: expert inputs scaled by the route's weight.
+int ftk_moe_gather_scaled(const void* h, int dtype, const int32_t* sorted_routes, const float* weights, int n_routes,
+                          int top_k, int hidden, void* out, void* stream);
+// x <- max(x, 0)^2 in place.
+int ftk_relu2(void* x, int dtype, long long n, void* stream);
+// Latent attention (latent.cu).  proj rows hold [query latent q_rank | key/value latent kv_rank | rotated key part
+// rot_dim]; cq_out [T, q_rank] gets the normed query latent, the token's cache row slab[slot_map[t]] (pad_dim wide)
+// [normed latent | rotated part | zeros].  n_rot leading dimensions of the part turn (pairs (2i, 2i+1) when
+// interleaved, else (i, i + n_rot/2)); table [max_pos, n_rot] = cos || sin.
+int ftk_latent_store(const void* proj, int dtype, long long row_stride, int q_rank, int kv_rank, int rot_dim, int n_rot,
+                     int interleaved, const float* wq, const float* wkv, float eps, const int32_t* positions,
+                     const float* table, int max_pos, void* cq_out, void* slab, long long slab_rows,
+                     const int32_t* slot_map, int pad_dim, int n_tokens, void* stream);
+// q [T, heads, flat_dim + rot_dim]: every head's rotated part goes, turned, to q_out[t, head, kv_rank : kv_rank + rot_dim]
+// (q_out [T, heads, pad_dim]; zeros behind it).
+int ftk_latent_query_rotate(const void* q, int dtype, int n_heads, int flat_dim, int rot_dim, int n_rot, int interleaved,
+                            const int32_t* positions, const float* table, int max_pos, void* q_out, int kv_rank,
+                            int pad_dim, int n_tokens, void* stream);
+// Matrix memory with exponential gates (mlstm.cu): see the file's header.  pre [T, 2 * heads] float32 = input gate
+// then forget gate before bias and cap; m_state [n_slots, heads]; gate_i, logit_f, m_out [T, heads].
+int ftk_mlstm_gates(const float* pre, const float* bias_i, const float* bias_f, float cap, float* m_state, int n_slots,
+                    const int32_t* state_slots, const int32_t* seg_info, int n_segs, int n_heads, int n_tokens,
+                    float* gate_i, float* logit_f, float* m_out, void* stream);
+// proj rows hold [q heads*dim | k heads*dim | v heads*vdim | ...]; q32, k32 [T, heads*dim], v32 [T, heads*(vdim+1)],
+// z [T, heads*dim] float32.
+int ftk_mlstm_prepare(const void* proj, int dtype, long long row_stride, int n_heads, int dim, int vdim,
+                      const float* gate_i, const float* logit_f, float* q32, float* k32, float* v32, float* z,
+                      int n_tokens, void* stream);
+// o32 [T, heads, vdim + 1] (the last column is n . q); out [T, heads * vdim] of `dtype`.
+int ftk_mlstm_output(const float* o32, const float* m, const void* gates, long long gate_stride, const float* norm_w,
+                     float eps, void* out, int dtype, int n_tokens, int n_heads, int vdim, void* stream);
 int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,
                     float limit, void* out, void* stream);
 int ftk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, void* stream);

@@ -61,11 +61,14 @@ struct AttnParams {
   // weights add up to less than one.  Added once per row, where the row is normalised (a split tile: in the merge).
   int has_sink;
   float sink;
+  // one sink logit per query head instead of `sink` (learned sinks); nullptr: `sink` for every head
+  const float* sink_heads;
 };
 
 // What the sink adds to a row's sum of exponentials taken relative to the maximum `m` (natural logarithm domain).
-__device__ __forceinline__ float sink_term(const AttnParams& p, float m) {
-  return p.has_sink ? expf(p.sink - m) : 0.f;
+// `head` is the row's query head.
+__device__ __forceinline__ float sink_term(const AttnParams& p, float m, int head) {
+  return p.has_sink ? expf((p.sink_heads ? __ldg(p.sink_heads + head) : p.sink) - m) : 0.f;
 }
 
 // Bias of a key `dist` positions behind the query, from the row of the query's head (`row` may be null).
@@ -223,7 +226,7 @@ __global__ void __launch_bounds__(kF32Rows * 32) attention_f32_kernel(AttnParams
   const int tok = it.q_start + it.tok0 + warp / G;
   if (it.nsplit == 1) {
     T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + warp % G) * D;
-    const float lt = l + sink_term(p, m);
+    const float lt = l + sink_term(p, m, kvh * G + warp % G);
     const float inv = lt > 0.f ? 1.f / lt : 0.f;
 #pragma unroll
     for (int i = 0; i < kPer; ++i) {
@@ -299,7 +302,7 @@ __global__ void __launch_bounds__(512) attention_merge_kernel(AttnParams p) {
       wgt[j] = w;
       L += lsum[j] * w;
     }
-    L = warp_sum(L) + sink_term(p, M);
+    L = warp_sum(L) + sink_term(p, M, kvh * G + r % G);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     const int tok = it.q_start + it.tok0 + r / G;
     T* o = (T*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
@@ -583,7 +586,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(AttnParams p) {
     __nv_bfloat16* out = (__nv_bfloat16*)p.out;
     // (the running maxima are in the exp2 domain)
     const float ln2e = 0.6931471805599453f;
-    const float t0 = l0 + sink_term(p, m0 * ln2e), t1 = l1 + sink_term(p, m1 * ln2e);
+    const float t0 = l0 + sink_term(p, m0 * ln2e, kvh * G + r0 % G), t1 = l1 + sink_term(p, m1 * ln2e, kvh * G + r1 % G);
     const float i0 = t0 > 0.f ? 1.f / t0 : 0.f, i1 = t1 > 0.f ? 1.f / t1 : 0.f;
     if (r0 < R) {
       __nv_bfloat16* dst = out + ((size_t)(it.q_start + it.tok0 + r0 / G) * p.Hq + kvh * G + r0 % G) * D;
@@ -654,7 +657,7 @@ __device__ __forceinline__ void merge_tile_rows_bf16(const AttnParams& p, const 
       L += sl[r * S + sp] * w;
       sm[r * S + sp] = w;
     }
-    L += sink_term(p, M);
+    L += sink_term(p, M, kvh * G + r % G);
     sinv[r] = L > 0.f ? 1.f / L : 0.f;
   }
   __syncthreads();
@@ -888,7 +891,7 @@ __global__ void __launch_bounds__(128) attention_decode_bf16_kernel(AttnParams p
     const int tok = it.q_start + it.tok0 + r / G;
     if (it.nsplit == 1) {
       __nv_bfloat16* out = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * D;
-      const float Lt = L + sink_term(p, M * ln2);
+      const float Lt = L + sink_term(p, M * ln2, kvh * G + r % G);
       out[d] = __float2bfloat16_rn(Lt > 0.f ? acc / Lt : 0.f);
     } else {
       const size_t slot = ((size_t)(it.base + it.split) * p.Hkv + kvh) * p.tile_rows + r;
@@ -1019,6 +1022,7 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   FTK_REQUIRE(!extras || extras->kv_split <= 1, "paged_attention_tc: KV heads are not split for the tcgen05 kernels");
   p.has_sink = extras ? extras->has_sink : 0;
   p.sink = extras ? extras->sink_logit : 0.f;
+  p.sink_heads = extras ? extras->sink_heads : nullptr;
   FTK_REQUIRE(!p.has_sink || (form == kTcSingle && !p.dist_bias),
               "paged_attention_tc: of the tcgen05 kernels the one with 128-row tiles takes a softmax sink");
   cudaStream_t s = (cudaStream_t)stream;
@@ -1119,6 +1123,7 @@ static int paged_attention_impl(const void* q, const void* k_slab, const void* v
   p.slab_heads = n_kv_heads; p.kv_split = 1;
   p.has_sink = extras ? extras->has_sink : 0;
   p.sink = extras ? extras->sink_logit : 0.f;
+  p.sink_heads = extras ? extras->sink_heads : nullptr;
   FTK_REQUIRE(!p.has_sink || !sel, "paged_attention: a sink cannot be combined with block selection");
   if (extras && extras->kv_split > 1) {
     FTK_REQUIRE(!sel && p.G % extras->kv_split == 0 && (long long)n_kv_heads * extras->kv_split <= 65535,

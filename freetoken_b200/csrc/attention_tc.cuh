@@ -781,7 +781,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int tok = it.q_start + it.tok0 + r / G;
       if (it.nsplit == 1) {
         // (a sink in the denominator: e^sink relative to the running maximum, which is in the exp2 domain)
-        const float lt = l + (p.has_sink ? exp2f(p.sink * 1.4426950408889634f - m_used) : 0.f);
+        const float lt = l + (p.has_sink ? exp2f((p.sink_heads ? __ldg(p.sink_heads + kvh * G + r % G) : p.sink) * 1.4426950408889634f - m_used) : 0.f);
         const float inv = lt > 0.f ? 1.f / lt : 0.f;
         __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * p.Hq + kvh * G + r % G) * kTcD;
 #pragma unroll 1

@@ -1,0 +1,175 @@
+// Matrix memory with exponential gates (the mLSTM of xLSTM) on top of the gated-linear-attention recurrence.
+//
+// Per head, with log gates i_t (input) and f_t (forget) and the running maximum m_t = max(f_t + m_(t-1), i_t), m_0 = 0:
+//   S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T,  n_t likewise with k_t alone,
+//   o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6).
+// With C_t = e^(m_t) S_t and N_t = e^(m_t) n_t this is the linear recurrence C_t = e^(f_t) C_(t-1) + (e^(i_t) k_t) v_t^T
+// (one decay per head) and o_t = C_t^T q_t / (max(|N_t . q_t|, 1) + 1e-6 e^(m_t)); N is the recurrence of one more
+// value column that is 1 for every token.  The gates are capped (|i_t| <= cap, f_t = logsigmoid of a capped
+// value), so C stays far inside the 32-bit range, and floating-point numbers keep their relative precision
+// under the change of scale.  Three kernels around the recurrence kernel:
+//   gates    per (request, head), a warp: the capped gates and m_t of the step's tokens (two warp scans per 32 tokens:
+//            F_t = f_1 + ... + f_t, m_t = F_t + max(m_0, max_(s <= t) (i_s - F_s))), m left in the request's slot;
+//   prepare  per token: q, e^(i_t) k and [v | 1] in 32-bit, the forget gate's logit once per key channel;
+//   output   per (token, head): the division, the head's unit norm, the weight, the sigmoid gate.
+#include "common.cuh"
+
+namespace ftk {
+
+__device__ __forceinline__ float capped(float x, float cap) { return cap * tanhf(x / cap); }
+__device__ __forceinline__ float log_sigmoid(float z) { return z > 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
+
+__global__ void mlstm_gates_kernel(const float* __restrict__ pre, const float* __restrict__ bias_i,
+                                   const float* __restrict__ bias_f, float cap, float* __restrict__ m_state, int n_slots,
+                                   const int32_t* __restrict__ state_slots, const int32_t* __restrict__ seg_info, int n_segs,
+                                   int H, int n_tokens, float* __restrict__ gate_i, float* __restrict__ logit_f,
+                                   float* __restrict__ m_out) {
+  pdl_wait();
+  pdl_trigger();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_segs * H) return;
+  const int seg = warp / H, h = warp - seg * H;
+  const int q_start = seg_info[seg * 4], q_len = seg_info[seg * 4 + 1], kv_len = seg_info[seg * 4 + 2];
+  if (q_start < 0 || q_len <= 0 || q_start + q_len > n_tokens) return;
+  const int slot = state_slots[seg];
+  const bool has_slot = slot >= 0 && slot < n_slots;
+  float m = (has_slot && kv_len > q_len) ? m_state[(size_t)slot * H + h] : 0.f;
+  for (int t0 = 0; t0 < q_len; t0 += 32) {
+    const int t = t0 + lane;
+    const bool on = t < q_len;
+    float gi = -INFINITY, f = 0.f, zf = 0.f;
+    if (on) {
+      const float* row = pre + (size_t)(q_start + t) * 2 * H;
+      gi = capped(row[h] + bias_i[h], cap);
+      zf = capped(row[H + h] + bias_f[h], cap);
+      f = log_sigmoid(zf);
+    }
+    float F = f;  // inclusive sum of the forget gates over the lanes
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, F, o);
+      if (lane >= o) F += v;
+    }
+    float best = on ? gi - F : -INFINITY;  // inclusive maximum of i_s - F_s
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, best, o);
+      if (lane >= o) best = fmaxf(best, v);
+    }
+    const float mt = F + fmaxf(m, best);
+    if (on) {
+      const size_t at = (size_t)(q_start + t) * H + h;
+      gate_i[at] = gi;
+      logit_f[at] = zf;
+      m_out[at] = mt;
+    }
+    const int last = min(31, q_len - t0 - 1);
+    m = __shfl_sync(0xffffffffu, mt, last);
+  }
+  if (has_slot && lane == 0) m_state[(size_t)slot * H + h] = m;
+}
+
+template <typename T>
+__global__ void mlstm_prepare_kernel(const T* __restrict__ proj, long long row_stride, int H, int D, int Dv,
+                                     const float* __restrict__ gate_i, const float* __restrict__ logit_f,
+                                     float* __restrict__ q32, float* __restrict__ k32, float* __restrict__ v32,
+                                     float* __restrict__ z) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const T* row = proj + (size_t)t * row_stride;
+  const int HD = H * D, HV = H * (Dv + 1);
+  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+    const int h = i / D;
+    q32[(size_t)t * HD + i] = to_float(row[i]);
+    k32[(size_t)t * HD + i] = expf(gate_i[(size_t)t * H + h]) * to_float(row[HD + i]);
+    z[(size_t)t * HD + i] = logit_f[(size_t)t * H + h];
+  }
+  for (int i = threadIdx.x; i < HV; i += blockDim.x) {
+    const int h = i / (Dv + 1), d = i - h * (Dv + 1);
+    v32[(size_t)t * HV + i] = d < Dv ? to_float(row[2 * HD + h * Dv + d]) : 1.f;
+  }
+}
+
+// a warp per (token, head)
+template <typename T>
+__global__ void mlstm_output_kernel(const float* __restrict__ o32, const float* __restrict__ m, const T* __restrict__ gates,
+                                    long long gate_stride, const float* __restrict__ norm_w, float eps, T* __restrict__ out,
+                                    int n_tokens, int H, int Dv) {
+  pdl_wait();
+  pdl_trigger();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_tokens * H) return;
+  const int t = warp / H, h = warp - t * H;
+  const float* src = o32 + ((size_t)t * H + h) * (Dv + 1);
+  const float den = fmaxf(fabsf(src[Dv]), 1.f) + 1e-6f * expf(m[(size_t)t * H + h]);
+  float ss = 0.f;
+  for (int d = lane; d < Dv; d += 32) {
+    const float v = src[d] / den;
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)Dv + eps);
+  const T* g = gates + (size_t)t * gate_stride + h * Dv;
+  T* dst = out + ((size_t)t * H + h) * Dv;
+  for (int d = lane; d < Dv; d += 32) {
+    const float v = src[d] / den * r * norm_w[h * Dv + d];
+    const float gate = 1.f / (1.f + expf(-to_float(g[d])));
+    dst[d] = from_float<T>(v * gate);
+  }
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_mlstm_gates(const float* pre, const float* bias_i, const float* bias_f, float cap, float* m_state,
+                               int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs, int n_heads,
+                               int n_tokens, float* gate_i, float* logit_f, float* m_out, void* stream) {
+  FTK_REQUIRE(n_segs >= 1 && n_heads >= 1 && n_tokens >= 0 && cap > 0.f, "mlstm_gates: bad sizes");
+  if (n_tokens == 0) return 0;
+  FTK_REQUIRE(pre && bias_i && bias_f && m_state && state_slots && seg_info && gate_i && logit_f && m_out,
+              "mlstm_gates: null pointer");
+  const int warps = n_segs * n_heads;
+  FTK_LAUNCH(mlstm_gates_kernel, (warps + 3) / 4, 128, 0, (cudaStream_t)stream, pre, bias_i, bias_f, cap, m_state, n_slots,
+             state_slots, seg_info, n_segs, n_heads, n_tokens, gate_i, logit_f, m_out);
+  FTK_LAUNCH_CHECK("mlstm_gates");
+  return 0;
+}
+
+extern "C" int ftk_mlstm_prepare(const void* proj, int dtype, long long row_stride, int n_heads, int dim, int vdim,
+                                 const float* gate_i, const float* logit_f, float* q32, float* k32, float* v32, float* z,
+                                 int n_tokens, void* stream) {
+  FTK_REQUIRE(dtype_ok(dtype) && n_heads >= 1 && dim >= 1 && vdim >= 1 && n_tokens >= 0, "mlstm_prepare: bad arguments");
+  if (n_tokens == 0) return 0;
+  FTK_REQUIRE(proj && gate_i && logit_f && q32 && k32 && v32 && z, "mlstm_prepare: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = n_heads * dim >= 1024 ? 256 : 128;
+  if (dtype == FTK_F32)
+    FTK_LAUNCH(mlstm_prepare_kernel<float>, n_tokens, threads, 0, s, (const float*)proj, row_stride, n_heads, dim, vdim, gate_i,
+               logit_f, q32, k32, v32, z);
+  else
+    FTK_LAUNCH(mlstm_prepare_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)proj, row_stride, n_heads, dim,
+               vdim, gate_i, logit_f, q32, k32, v32, z);
+  FTK_LAUNCH_CHECK("mlstm_prepare");
+  return 0;
+}
+
+extern "C" int ftk_mlstm_output(const float* o32, const float* m, const void* gates, long long gate_stride,
+                                const float* norm_w, float eps, void* out, int dtype, int n_tokens, int n_heads, int vdim,
+                                void* stream) {
+  FTK_REQUIRE(dtype_ok(dtype) && n_heads >= 1 && vdim >= 1 && n_tokens >= 0, "mlstm_output: bad arguments");
+  if (n_tokens == 0) return 0;
+  FTK_REQUIRE(o32 && m && gates && norm_w && out, "mlstm_output: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long warps = (long long)n_tokens * n_heads;
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  if (dtype == FTK_F32)
+    FTK_LAUNCH(mlstm_output_kernel<float>, blocks, 128, 0, s, o32, m, (const float*)gates, gate_stride, norm_w, eps, (float*)out,
+               n_tokens, n_heads, vdim);
+  else
+    FTK_LAUNCH(mlstm_output_kernel<__nv_bfloat16>, blocks, 128, 0, s, o32, m, (const __nv_bfloat16*)gates, gate_stride, norm_w,
+               eps, (__nv_bfloat16*)out, n_tokens, n_heads, vdim);
+  FTK_LAUNCH_CHECK("mlstm_output");
+  return 0;
+}

@@ -32,7 +32,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, int n
   // the order, and dividing by the chosen experts' sum below leaves the softmax over them alone
   const float* pre = scoring == FTK_SCORE_SOFTMAX_OF_CHOSEN ? bias : nullptr;
   if (pre) bias = nullptr;
-  if (scoring == FTK_SCORE_SIGMOID) {
+  if (scoring == FTK_SCORE_SIGMOID || scoring == FTK_SCORE_SIGMOID_RAW) {
     for (int e = lane; e < n_experts; e += 32) s[e] = 1.f / (1.f + expf(-logit_of(row, e, n_experts, n_parts)));
   } else {
     float mx = -INFINITY;
@@ -80,7 +80,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, int n
     }
     __syncwarp();
   }
-  const float denom = scoring == FTK_SCORE_SIGMOID ? wsum + 1e-20f : wsum;
+  const float denom = scoring == FTK_SCORE_SIGMOID_RAW ? 1.f : scoring == FTK_SCORE_SIGMOID ? wsum + 1e-20f : wsum;  // (raw: the scores as they are)
   for (int j = lane; j < top_k; j += 32) weights[j] = weights[j] / denom * scale;
 }
 
@@ -116,7 +116,7 @@ __device__ __forceinline__ void route_token_regs(const float* __restrict__ row, 
     }
     bias = nullptr;
   }
-  if (scoring == FTK_SCORE_SIGMOID) {
+  if (scoring == FTK_SCORE_SIGMOID || scoring == FTK_SCORE_SIGMOID_RAW) {
 #pragma unroll
     for (int q = 0; q < PER; ++q) sv[q] = 1.f / (1.f + expf(-sv[q]));
   } else {
@@ -173,7 +173,7 @@ __device__ __forceinline__ void route_token_regs(const float* __restrict__ row, 
     }
   }
   __syncwarp();
-  const float denom = scoring == FTK_SCORE_SIGMOID ? wsum + 1e-20f : wsum;
+  const float denom = scoring == FTK_SCORE_SIGMOID_RAW ? 1.f : scoring == FTK_SCORE_SIGMOID ? wsum + 1e-20f : wsum;  // (raw: the scores as they are)
   for (int j = lane; j < top_k; j += 32) weights[j] = wbuf[j] / denom * scale;
   __syncwarp();
 }
@@ -363,7 +363,7 @@ using namespace ftk;
 extern "C" int ftk_router_topk(const float* logits, int n_parts, const float* bias, int n_tokens, int n_experts, int top_k,
                                int scoring, float scale, int32_t* ids, float* weights, void* stream) {
   FTK_REQUIRE(n_parts >= 1 && n_parts <= 4, "router_topk: %d blocks of logits per token (1 to 4)", n_parts);
-  FTK_REQUIRE(scoring >= FTK_SCORE_SIGMOID && scoring <= FTK_SCORE_SOFTMAX_OF_CHOSEN, "router_topk: unknown scoring %d", scoring);
+  FTK_REQUIRE(scoring >= FTK_SCORE_SIGMOID && scoring <= FTK_SCORE_SIGMOID_RAW, "router_topk: unknown scoring %d", scoring);
   FTK_REQUIRE(n_experts >= 1 && top_k >= 1 && top_k <= n_experts, "router_topk: top_k=%d of %d experts", top_k, n_experts);
   FTK_REQUIRE(n_tokens >= 0, "router_topk: bad token count");
   if (n_tokens == 0) return 0;
@@ -392,7 +392,7 @@ extern "C" int ftk_moe_route(const float* x, const float* gate_w, const float* b
                              int n_experts, int top_k, int scoring, float scale, float* logits, int32_t* ids,
                              float* weights, int32_t* counts, int32_t* offsets, int32_t* routes, int32_t* pos,
                              int do_sort, void* stream) {
-  FTK_REQUIRE(scoring >= FTK_SCORE_SIGMOID && scoring <= FTK_SCORE_SOFTMAX_OF_CHOSEN, "moe_route: unknown scoring %d", scoring);
+  FTK_REQUIRE(scoring >= FTK_SCORE_SIGMOID && scoring <= FTK_SCORE_SIGMOID_RAW, "moe_route: unknown scoring %d", scoring);
   FTK_REQUIRE(ftk_moe_route_fits(n_tokens, hidden, n_experts, top_k),
               "moe_route: %d tokens, width %d, %d experts, top %d do not fit the one-launch routing (at most 32 tokens, "
               "a width that is a multiple of 4); use the matrix product + router_topk + moe_permute",

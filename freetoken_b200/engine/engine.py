@@ -141,13 +141,15 @@ class Engine:
             if num_pages < 1:
                 raise ConfigError("no memory left for the cache after loading the model")
         self.num_pages = int(num_pages)
-        self.cache = CacheManager(needs, config.page_size, self.num_pages, config.max_running_req,
+        block_needs = self.model.block_state_needs()  # blocks with a state of their own: slots beside the mixers'
+        self.cache = CacheManager(list(needs) + [(("block", i), n) for i, n in block_needs], config.page_size, self.num_pages, config.max_running_req,
                                   self.max_seq_len, self.dtype, self.device,
                                   max_step_tokens=self.max_step_tokens)
         self._views: List[Any] = []
         for i, e in enumerate(spec.schedule):
             owner = i if e.cache_from is None else e.cache_from
             self._views.append(self.cache.view(owner))
+        self._block_views: Dict[int, Any] = {i: self.cache.view(("block", i)) for i, _ in block_needs}
         self.buffers = StepBuffers(self.device, self._metadata_capacity())
         self.graphs: Dict[Any, Any] = {}
         self.graph_logits: Dict[Any, torch.Tensor] = {}
@@ -157,7 +159,7 @@ class Engine:
         # (a mixer that keeps a state cannot repeat a step, but its step can still be recorded when everything
         # it does is decided on the device: it says so with ``graph_recordable``; the step that records then
         # takes its result from the warm-up run and is not replayed)
-        mixers = self.model.mixers()
+        mixers = self.model.stateful_parts()
         self.use_graphs = (bool(config.cuda_graph) and self.device.type == "cuda"
                            and all(getattr(m, "graph_safe", False) or getattr(m, "graph_recordable", False)
                                    for m in mixers))
@@ -333,7 +335,8 @@ class Engine:
             n_tokens=T, segments=segments, token_ids=tensors["token_ids"],
             positions=tensors["positions"], seg_info=tensors["seg_info"],
             state_slots=tensors["state_slots"], logit_rows=tensors["logit_rows"],
-            n_logit_rows=len(logit_rows), attention_plans=plans, decode_only=decode_only)
+            n_logit_rows=len(logit_rows), attention_plans=plans, decode_only=decode_only,
+            block_states=self._block_views)
         step.extras["tensors"] = tensors
         views = self._step_views(tensors)
 

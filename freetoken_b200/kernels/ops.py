@@ -39,7 +39,7 @@ long steps and decode steps), 256 (the same with two query tiles per CTA: very l
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Sequence
+from typing import Any, Optional, Sequence
 
 import torch
 
@@ -50,7 +50,8 @@ F32, BF16 = 0, 1
 ACT_SILU, ACT_SWIGLUOAI = 0, 1
 SCORE_SIGMOID, SCORE_SOFTMAX, SCORE_SOFTMAX_OF_CHOSEN = 0, 1, 2
 ACT_CODES = {"silu": ACT_SILU, "swigluoai": ACT_SWIGLUOAI}
-SCORE_CODES = {"sigmoid": SCORE_SIGMOID, "softmax": SCORE_SOFTMAX, "softmax_of_chosen": SCORE_SOFTMAX_OF_CHOSEN}
+SCORE_CODES = {"sigmoid": SCORE_SIGMOID, "softmax": SCORE_SOFTMAX, "softmax_of_chosen": SCORE_SOFTMAX_OF_CHOSEN,
+               "sigmoid_raw": 3}
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -74,7 +75,8 @@ class _StreamNorm(ctypes.Structure):
 
 
 class _AttnExtras(ctypes.Structure):
-    _fields_ = [("dist_bias", _vp), ("dist_len", _i), ("kv_split", _i), ("has_sink", _i), ("sink_logit", _f)]
+    _fields_ = [("dist_bias", _vp), ("dist_len", _i), ("kv_split", _i), ("has_sink", _i), ("sink_logit", _f),
+                ("sink_heads", _vp)]
 
 
 _SIGNATURES = {
@@ -133,6 +135,16 @@ _SIGNATURES = {
     "ftk_softcap_f32": [_vp, ctypes.c_longlong, _f, _vp],
     "ftk_postnorm_add_norm": [_vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _vp, _f, _i, _vp, _vp, _vp, _i, _i, _vp],
     "ftk_gated_heads": [_vp, _i, _i, _vp, ctypes.c_longlong, _vp, _f, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "ftk_short_conv": [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "ftk_depth_mix": [_vp, ctypes.c_longlong, _i, _vp, _vp, ctypes.c_longlong, _vp],
+    "ftk_moe_gather_scaled": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "ftk_relu2": [_vp, _i, ctypes.c_longlong, _vp],
+    "ftk_latent_store": [_vp, _i, ctypes.c_longlong, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp,
+                         ctypes.c_longlong, _vp, _i, _i, _vp],
+    "ftk_latent_query_rotate": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "ftk_mlstm_gates": [_vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "ftk_mlstm_prepare": [_vp, _i, ctypes.c_longlong, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
+    "ftk_mlstm_output": [_vp, _vp, _vp, ctypes.c_longlong, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "ftk_gla_scan": [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _i, _vp, _vp, _f, _f,
                      _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
 }
@@ -416,7 +428,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                     part_ml: Optional[torch.Tensor], out: torch.Tensor, tile_rows: int, scale: float,
                     window: Optional[int], sel: Optional[torch.Tensor] = None, block_size: int = 0,
                     few_rows: bool = False, dist_bias: Optional[torch.Tensor] = None, kv_split: int = 1,
-                    sink: Optional[float] = None) -> None:
+                    sink: Any = None) -> None:
     """Causal softmax attention of the step's queries over the paged keys and values.
 
     ``q, out [T, Hq, D]``; slabs ``[pages, Hkv, page_size, D]``; ``block_table [rows, width]``
@@ -444,8 +456,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     Of the tcgen05 kernels the ones with one query tile a piece (128 rows, or at most 16) take the bias; with
     one slab for keys and values their key tile in shared memory serves both products.
 
-    ``sink`` (a logit, or None): the softmax's denominator also holds ``e^sink``, a key without a value, so a
-    row's weights are ``e^(s_j) / (e^sink + sum_i e^(s_i))``.  A tile that is split along the keys gets it once,
+    ``sink`` (a logit, a float32 tensor ``[Hq]`` of one logit per query head, or None): the softmax's denominator
+    also holds ``e^sink``, a key without a value, so a row's weights are ``e^(s_j) / (e^sink + sum_i e^(s_i))``.  A tile that is split along the keys gets it once,
     in the merge.  Not with block selection.  Of the tcgen05 kernels the one with 128-row tiles takes a window and a
     sink (its work list then starts every piece on a key tile: ``build_plan(..., window, key_tile=128)``).
     """
@@ -456,6 +468,11 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     if out.shape != q.shape or out.dtype != q.dtype or k_slab.dtype != q.dtype:
         raise KernelError("paged_attention: dtypes or out shape do not agree")
     n_slots = part_o.shape[0] if part_o is not None else 0
+    sink_heads = None
+    if isinstance(sink, torch.Tensor):
+        if sink.shape != (Hq,):
+            raise KernelError("paged_attention: a sink per head must be [Hq]")
+        sink_heads, sink = _dev(sink, "sink", torch.float32), 0.0
     kv_split = max(1, int(kv_split))
     Hv = Hkv * kv_split
     if kv_split > 1 and ((Hq // Hkv) % kv_split or sel is not None or tile_rows in (128, 256) or few_rows):
@@ -470,10 +487,10 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         if sel is not None or q.dtype != torch.bfloat16:
             raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without block selection")
         if window or sink is not None:  # the form with one 128-row query tile a piece takes both
-            if tile_rows != 128 or few_rows or dist_bias is not None or v_slab.data_ptr() == k_slab.data_ptr():
+            if tile_rows != 128 or few_rows or dist_bias is not None or (window and v_slab.data_ptr() == k_slab.data_ptr()):
                 raise KernelError("paged_attention: of the tcgen05 kernels the one with 128-row tiles takes a window or a "
                                   "sink (values of their own, no distance bias)")
-            ex = _AttnExtras(None, 0, 1, 0 if sink is None else 1, 0.0 if sink is None else float(sink))
+            ex = _AttnExtras(None, 0, 1, 0 if sink is None else 1, 0.0 if sink is None else float(sink), sink_heads)
             _check(_lib().ftk_paged_attention_tc_ex(
                 _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
                 _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -488,7 +505,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
             if tile_rows == 256 or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
                 raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "
                                   "distance bias [Hq, L]")
-            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1], 1, 0, 0.0)
+            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1], 1, 0, 0.0, None)
             _check(_lib().ftk_paged_attention_tc_ex(
                 _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
                 _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -529,7 +546,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         if dist_bias is not None and (dist_bias.dim() != 2 or dist_bias.shape[0] != Hq or dist_bias.shape[1] < 1):
             raise KernelError("paged_attention: dist_bias must be [Hq, L]")
         ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1] if dist_bias is not None else 0,
-                         kv_split, 0 if sink is None else 1, 0.0 if sink is None else float(sink))
+                         kv_split, 0 if sink is None else 1, 0.0 if sink is None else float(sink), sink_heads)
         _check(_lib().ftk_paged_attention_ex(
             _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"), _code(q, "q"),
             _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -1087,3 +1104,162 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         _dev(seg_chunks, "seg_chunks", torch.int32), 1 if any_single else 0, 1 if any_multi else 0,
         _dev(carry, "carry", torch.float32), _dev(decay_prod, "decay_prod", torch.float32),
         _dev(out, "out", torch.float32), T, H, D, Dv, _stream()), "gla_scan", max(1, launches))
+
+
+# --------------------------------------------------------------------------- short convolution, depth mix
+def short_conv(x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], state_slots: torch.Tensor,
+               seg_info: torch.Tensor, n_segs: int, out: torch.Tensor) -> None:
+    """``out[t] = x[t] + sum_j w[:, j] * in(t - taps + 1 + j)`` over each request's own inputs (a causal
+    convolution over time on every channel, plus the input itself): ``x [T, C]`` float32 (the stream),
+    ``w [C, taps]`` float32, ``out [T, C]`` of the engine's dtype.  The request's last ``taps - 1`` inputs live in
+    ``state [slots, taps - 1, C]`` (float32, oldest first) at ``state_slots[segment]``: read for the step's first
+    tokens (zeros for a request whose first tokens these are) and replaced by the step's last inputs."""
+    T, C = x.shape
+    taps = w.shape[1]
+    if w.shape != (C, taps) or out.shape != (T, C) or x.dtype != torch.float32:
+        raise KernelError("short_conv: x [T, C] float32, w [C, taps], out [T, C] expected")
+    if taps > 1 and (state is None or state.shape[1:] != (taps - 1, C)):
+        raise KernelError("short_conv: state must be [slots, taps - 1, C]")
+    _check(_lib().ftk_short_conv(
+        _dev(x, "x", torch.float32), _dev(w, "w", torch.float32), taps, _dev(state, "state", torch.float32),
+        state.shape[0] if state is not None else 0, _dev(state_slots, "state_slots", torch.int32),
+        _dev(seg_info, "seg_info", torch.int32), n_segs, _dev(out, "out"), _code(out, "out"), T, C, _stream()),
+        "short_conv")
+
+
+def depth_mix(hist: torch.Tensor, n_prev: int, mix: torch.Tensor, x: torch.Tensor) -> None:
+    """``hist[n_prev] = x``, then ``x = sum_{j <= n_prev} mix[j] * hist[j]``: ``hist [layers, cap, C]`` float32 keeps
+    every layer's output for the step's tokens (rows ``[:T]`` of each are used), ``x [T, C]`` float32."""
+    T, C = x.shape
+    if hist.dim() != 3 or hist.shape[2] != C or hist.shape[1] < T or hist.shape[0] <= n_prev or mix.numel() < n_prev + 1:
+        raise KernelError("depth_mix: shapes do not agree")
+    _check(_lib().ftk_depth_mix(_dev(hist, "hist", torch.float32), hist.stride(0), int(n_prev),
+                                _dev(mix, "mix", torch.float32), _dev(x, "x", torch.float32), T * C, _stream()),
+           "depth_mix")
+
+
+def moe_gather_scaled(h: torch.Tensor, sorted_routes: torch.Tensor, weights: torch.Tensor, top_k: int,
+                      out: torch.Tensor) -> None:
+    """``out[r, :] = weights[sorted_routes[r]] * h[sorted_routes[r] // top_k, :]`` (32-bit product, rounded once):
+    expert inputs in expert order, each scaled by its route's weight (``weights [T * top_k]`` float32)."""
+    T, H = h.shape
+    R = sorted_routes.numel()
+    if out.shape != (R, H) or out.dtype != h.dtype or weights.numel() != R:
+        raise KernelError("moe_gather_scaled: out must be [routes, hidden] of h's dtype, one weight per route")
+    _check(_lib().ftk_moe_gather_scaled(_dev(h, "h"), _code(h, "h"), _dev(sorted_routes, "sorted_routes", torch.int32),
+                                        _dev(weights, "weights", torch.float32), R, top_k, H, _dev(out, "out"),
+                                        _stream()), "moe_gather_scaled")
+
+
+def relu2_(x: torch.Tensor) -> None:
+    """``x <- max(x, 0)^2`` in place."""
+    _check(_lib().ftk_relu2(_dev(x, "x"), _code(x, "x"), x.numel(), _stream()), "relu2")
+
+
+# --------------------------------------------------------------------------- latent attention
+def latent_store(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, n_rot: int, interleaved: bool,
+                 wq: torch.Tensor, wkv: torch.Tensor, eps: float, positions: torch.Tensor,
+                 rope_table: Optional[torch.Tensor], cq_out: torch.Tensor, slab: torch.Tensor,
+                 slot_map: torch.Tensor) -> None:
+    """From the rows ``proj [T, q_rank + kv_rank + rot_dim]`` of a latent-attention layer's input projection:
+    ``cq_out [T, q_rank]`` gets the RMS-normed query latent (weight ``wq``); the token's cache row of
+    ``slab [pages, 1, page_size, pad]`` at ``slot_map[t]`` gets ``[RMS-normed key/value latent (weight wkv) | the
+    shared key part turned by the token's position | zeros]``.  The first ``n_rot`` dimensions of the part turn,
+    in pairs ``(2i, 2i + 1)`` when ``interleaved`` and ``(i, i + n_rot / 2)`` otherwise, by the angles of
+    ``rope_table [positions, n_rot]`` (``cos || sin``).  A token whose slot is negative stores nothing."""
+    T = proj.shape[0]
+    width = q_rank + kv_rank + rot_dim
+    if proj.shape != (T, width) or proj.stride(1) != 1 or cq_out.shape != (T, q_rank) or not cq_out.is_contiguous():
+        raise KernelError("latent_store: proj [T, q_rank + kv_rank + rot_dim], cq_out [T, q_rank] expected")
+    if slab.dim() != 4 or slab.shape[1] != 1 or slab.shape[3] < kv_rank + rot_dim or slab.dtype != proj.dtype \
+            or cq_out.dtype != proj.dtype or not slab.is_contiguous():
+        raise KernelError("latent_store: slab must be [pages, 1, page_size, >= kv_rank + rot_dim] of proj's dtype")
+    if n_rot and (rope_table is None or rope_table.shape[1] != n_rot):
+        raise KernelError("latent_store: the rotation table must be [positions, n_rot]")
+    _check(_lib().ftk_latent_store(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.stride(0) if T > 1 else width, q_rank, kv_rank, rot_dim, n_rot,
+        1 if interleaved else 0, _dev(wq, "wq", torch.float32), _dev(wkv, "wkv", torch.float32), float(eps),
+        _dev(positions, "positions", torch.int32), _dev(rope_table, "rope_table", torch.float32),
+        rope_table.shape[0] if rope_table is not None else 1, _dev(cq_out, "cq_out"), _dev(slab, "slab"),
+        slab.shape[0] * slab.shape[2], _dev(slot_map, "slot_map", torch.int32), slab.shape[3], T, _stream()),
+        "latent_store")
+
+
+def latent_query_rotate(q: torch.Tensor, flat_dim: int, rot_dim: int, n_rot: int, interleaved: bool,
+                        positions: torch.Tensor, rope_table: Optional[torch.Tensor], q_out: torch.Tensor,
+                        kv_rank: int) -> None:
+    """``q [T, H, flat_dim + rot_dim]``: every head's last ``rot_dim`` values, turned by the token's position (see
+    :func:`latent_store`), go to ``q_out[t, h, kv_rank : kv_rank + rot_dim]``; the columns behind them are zeroed
+    (``q_out [T, H, pad]``; its first ``kv_rank`` columns are left alone)."""
+    T, H, qd = q.shape
+    if qd != flat_dim + rot_dim or q_out.shape[:2] != (T, H) or q_out.shape[2] < kv_rank + rot_dim \
+            or q_out.dtype != q.dtype or not q.is_contiguous() or not q_out.is_contiguous():
+        raise KernelError("latent_query_rotate: shapes or dtypes do not agree")
+    _check(_lib().ftk_latent_query_rotate(
+        _dev(q, "q"), _code(q, "q"), H, flat_dim, rot_dim, n_rot, 1 if interleaved else 0,
+        _dev(positions, "positions", torch.int32), _dev(rope_table, "rope_table", torch.float32),
+        rope_table.shape[0] if rope_table is not None else 1, _dev(q_out, "q_out"), kv_rank, q_out.shape[2], T,
+        _stream()), "latent_query_rotate")
+
+
+def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """A product per head: ``out[t, h, :] = x[t, h, :] @ w[h]`` with ``x [T, H, K]``, ``w [H, K, N]``, ``out [T, H, N]``.
+    ``x`` and ``out`` may be views of the leading columns of wider heads (last stride 1): the library's batched
+    product reads and writes them where they lie."""
+    T, H, K = x.shape
+    if w.shape[:2] != (H, K) or out.shape != (T, H, w.shape[2]) or x.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("heads_linear: shapes do not agree")
+    torch.bmm(x.transpose(0, 1), w, out=out.transpose(0, 1))
+
+
+# --------------------------------------------------------------------------- matrix memory with exponential gates
+def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, m_state: torch.Tensor,
+                state_slots: torch.Tensor, seg_info: torch.Tensor, n_segs: int, gate_i: torch.Tensor,
+                logit_f: torch.Tensor, m_out: torch.Tensor) -> None:
+    """Gates of a matrix-memory layer for the step's tokens, per (request, head), all float32:
+    ``gate_i = cap tanh((pre_i + b_i) / cap)``, ``logit_f = cap tanh((pre_f + b_f) / cap)`` (the forget gate is
+    ``logsigmoid(logit_f)``), and the running maximum ``m_t = max(f_t + m_(t-1), i_t)``, which starts from
+    ``m_state[slot, head]`` (from 0 for a request's first tokens) and is left there.  ``pre [T, 2 H]``."""
+    T, H2 = pre.shape
+    H = H2 // 2
+    if gate_i.shape != (T, H) or logit_f.shape != (T, H) or m_out.shape != (T, H) or m_state.shape[1:] != (H,):
+        raise KernelError("mlstm_gates: shapes do not agree")
+    _check(_lib().ftk_mlstm_gates(
+        _dev(pre, "pre", torch.float32), _dev(bias_i, "bias_i", torch.float32), _dev(bias_f, "bias_f", torch.float32),
+        float(cap), _dev(m_state, "m_state", torch.float32), m_state.shape[0],
+        _dev(state_slots, "state_slots", torch.int32), _dev(seg_info, "seg_info", torch.int32), n_segs, H, T,
+        _dev(gate_i, "gate_i", torch.float32), _dev(logit_f, "logit_f", torch.float32),
+        _dev(m_out, "m_out", torch.float32), _stream()), "mlstm_gates")
+
+
+def mlstm_prepare(proj: torch.Tensor, n_heads: int, dim: int, vdim: int, gate_i: torch.Tensor, logit_f: torch.Tensor,
+                  q32: torch.Tensor, k32: torch.Tensor, v32: torch.Tensor, z: torch.Tensor) -> None:
+    """Inputs of the linear recurrence that a matrix-memory layer runs on, all float32: ``q32 = q``,
+    ``k32 = e^(gate_i) k``, ``v32 = [v | 1]`` per head (the extra column carries the normaliser), ``z`` the forget
+    gate's logit once per key channel.  ``proj [T, >= H (2 dim + vdim)]`` holds q, k, v side by side."""
+    T = proj.shape[0]
+    H = n_heads
+    if proj.shape[1] < H * (2 * dim + vdim) or proj.stride(1) != 1 or q32.shape != (T, H * dim) \
+            or k32.shape != (T, H * dim) or v32.shape != (T, H * (vdim + 1)) or z.shape != (T, H * dim):
+        raise KernelError("mlstm_prepare: shapes do not agree")
+    _check(_lib().ftk_mlstm_prepare(
+        _dev(proj, "proj"), _code(proj, "proj"), proj.stride(0) if T > 1 else proj.shape[1], H, dim, vdim,
+        _dev(gate_i, "gate_i", torch.float32), _dev(logit_f, "logit_f", torch.float32), _dev(q32, "q32", torch.float32),
+        _dev(k32, "k32", torch.float32), _dev(v32, "v32", torch.float32), _dev(z, "z", torch.float32), T, _stream()),
+        "mlstm_prepare")
+
+
+def mlstm_output(o32: torch.Tensor, m: torch.Tensor, gates: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                 out: torch.Tensor) -> None:
+    """``o32 [T, H, vdim + 1]`` (numerator columns and ``n . q``), ``m [T, H]``: ``o = num / (max(|n . q|, 1) +
+    1e-6 e^m)``, divided by its root mean square over the head, times ``norm_weight [H * vdim]``, times
+    ``sigmoid(gates)`` (``gates [T, H * vdim]``, a view of adjacent columns is fine) into ``out [T, H * vdim]``."""
+    T, H, dv1 = o32.shape
+    Dv = dv1 - 1
+    if out.shape != (T, H * Dv) or gates.shape != (T, H * Dv) or gates.stride(1) != 1 or gates.dtype != out.dtype \
+            or norm_weight.numel() != H * Dv or m.shape != (T, H) or not out.is_contiguous():
+        raise KernelError("mlstm_output: shapes or dtypes do not agree")
+    _check(_lib().ftk_mlstm_output(
+        _dev(o32, "o32", torch.float32), _dev(m, "m", torch.float32), gates.data_ptr(),
+        gates.stride(0) if T > 1 else H * Dv, _dev(norm_weight, "norm_weight", torch.float32), float(eps),
+        _dev(out, "out"), _code(out, "out"), T, H, Dv, _stream()), "mlstm_output")

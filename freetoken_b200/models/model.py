@@ -98,8 +98,21 @@ class Model:
                     out.append((i, need))
         return out
 
+    def block_state_needs(self) -> List[Tuple[int, Any]]:
+        """(schedule entry, need) for every entry whose block keeps a per-request state of its own."""
+        out = []
+        for i, e in enumerate(self.spec.schedule):
+            need = self.blocks[e.layer].state_need()
+            if need is not None:
+                out.append((i, need))
+        return out
+
     def mixers(self):
         return [b.mixer for b in self.blocks]
+
+    def stateful_parts(self):
+        """Mixers, and blocks that keep a state: what decides whether a step may be replayed from a graph."""
+        return self.mixers() + [b for b in self.blocks if b.state_need() is not None]
 
     def parts(self) -> List[Part]:
         """Every part of the model, each once (parts shared through ``env.shared`` included)."""
@@ -156,6 +169,7 @@ class Model:
                     x.add_rows_of(self.embedding.table(), step.token_ids)
                 if e.add_pass_vector is not None:
                     x.add_vector(self.pass_vectors.vector(e.add_pass_vector))
+            step.entry = i
             with nvtx_range(f"layer {e.layer}"):
                 x = self.blocks[e.layer].forward(x, residual, step, cache_views[i], e.cache_from is None)
         R = step.n_logit_rows

@@ -401,6 +401,11 @@ class Block(Part):
         self.mixer_name = mixer_name
         self.ffn_name = ffn_name
 
+    def state_need(self) -> CacheNeed:
+        """Per-request state of the block itself (beside its mixer's cache): a ``StateNeed`` or None.  The engine
+        keeps it in the cache manager's state slots and hands the view over in ``step.block_states[step.entry]``."""
+        return None
+
     def forward(self, x: Optional[torch.Tensor], residual: torch.Tensor, step: "StepState",
                 cache: Any, writes_cache: bool) -> torch.Tensor:
         """Consume the previous layer's output ``x`` (None for the first layer) and the
@@ -441,3 +446,5 @@ class StepState:
     extras: Dict[str, Any] = field(default_factory=dict)
     decode_only: bool = False  # every segment brings exactly one token
     capturing: bool = False  # the step is being recorded into a CUDA graph
+    entry: int = 0  # the schedule entry whose layer is running (set by the model)
+    block_states: Dict[int, Any] = field(default_factory=dict)  # schedule entry -> state view of its block

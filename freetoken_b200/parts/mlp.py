@@ -1,5 +1,8 @@
 """Dense gated feed-forward: ``down(act(gate(h), up(h)))``.
 
+``dense_mlp`` is the plain two-matrix form ``down(act(up(h) + b_up)) + b_down`` with ``act = relu(z)^2``; the biases
+join the 32-bit sums of the library's products.
+
 ``gate_up_proj`` holds the gate rows then the up rows; the activation works on the two
 un-interleaved halves (python/freetoken/models/minimax_m3/mlp.py:54-59).  ``silu`` is
 ``g sigmoid(g) u``; ``swigluoai`` clamps first: ``g' = min(g, limit)``,
@@ -56,4 +59,42 @@ class GatedMLP(FeedForward):
         ops.act_and_mul(gu, a, self.act, self.alpha, self.limit)
         out = ws.get(f"{self.tag}.out", (T, self.hidden), dt, (cap, self.hidden))
         ops.linear(a, self.params["down_proj.weight"], out)
+        return out
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """params: ``hidden``, ``inter``, ``act`` ("relu2"), ``bias`` (bool), ``init_std``."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden"])
+        self.inter = int(spec["inter"])
+        self.act = spec.get("act", "relu2")
+        if self.act != "relu2":
+            raise ConfigError(f"dense_mlp: unknown activation '{self.act}'")
+        self.has_bias = bool(spec.get("bias", True))
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        std = self.spec.get("init_std")
+        std_in, std_out = (float(std[0]), float(std[1])) if std else (0.02, 0.02)
+        out = {"up_proj.weight": ParamSpec((self.inter, self.hidden), init=("normal", 0.0, std_in)),
+               "down_proj.weight": ParamSpec((self.hidden, self.inter), init=("normal", 0.0, std_out))}
+        if self.has_bias:
+            out["up_proj.bias"] = ParamSpec((self.inter,), init=("normal", 0.0, 0.5 if std else 0.02))
+            out["down_proj.bias"] = ParamSpec((self.hidden,), init=("normal", 0.0, 0.5 if std else 0.02))
+        return out
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        return n_tokens * (self.inter + self.hidden) * item
+
+    def forward(self, h: torch.Tensor, step: StepState, h_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T = h.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        a = ws.get("dense_mlp.act", (T, self.inter), dt, (cap, self.inter))
+        ops.linear(h, self.params["up_proj.weight"], a, self.params.get("up_proj.bias"))
+        ops.relu2_(a)
+        out = ws.get("dense_mlp.out", (T, self.hidden), dt, (cap, self.hidden))
+        ops.linear(a, self.params["down_proj.weight"], out, self.params.get("down_proj.bias"))
         return out

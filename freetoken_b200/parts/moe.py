@@ -13,6 +13,11 @@ product with ``gate_up_proj [E, 2I, H]``, activation on the two halves, grouped 
 route order with a 32-bit accumulator (:111-153).  The shared expert runs on the same input
 and is added (moe.py:87-88).
 
+``weight_on="input"``: a route's weight multiplies the expert's input instead of its output, ``sum_j expert_j(w_j h)``
+(the experts are not linear, so this is another function): the rows are scaled while they are copied into expert
+order, and the second product's weights are 1.  ``scoring="sigmoid_raw"`` leaves the chosen experts' sigmoid
+scores as they are (no division by their sum).  The reference has neither.
+
 ``router="token_table"`` has no router matrix: a table ``[vocab, top_k]`` of expert ids (the ids of a
 row differ) names each token id's experts, each with weight ``1 / top_k``; the expert products are
 the same kernels.  The reference has no such router.
@@ -60,7 +65,7 @@ class MoE(FeedForward):
     """params: ``hidden``, ``inter``, ``n_experts``, ``top_k``, ``scoring`` ("sigmoid" |
     "softmax"), ``bias`` (bool), ``scale``, ``act``, ``alpha``, ``limit``,
     ``shared_inter`` (0 = no shared expert), ``shared_limit`` (the shared expert's clamp; ``limit`` when absent), ``router`` ("learned" | "token_table"; the table also needs
-    ``vocab``).  ``h_f32`` given to the forward calls of a bfloat16 model
+    ``vocab``), ``weight_on`` ("output" | "input").  ``h_f32`` given to the forward calls of a bfloat16 model
     is ``float32(h)``, as a norm's ``out_f32`` is."""
 
     wants_f32_input = True
@@ -85,6 +90,11 @@ class MoE(FeedForward):
         self.router = spec.get("router", "learned")
         if self.router not in ("learned", "token_table"):
             raise ConfigError(f"moe: unknown router '{self.router}'")
+        self.weight_on = spec.get("weight_on", "output")
+        if self.weight_on not in ("output", "input"):
+            raise ConfigError(f"moe: weight_on must be 'output' or 'input', got '{self.weight_on}'")
+        self.on_input = self.weight_on == "input"
+        self._ones: Optional[torch.Tensor] = None
         self.by_table = self.router == "token_table"
         self.vocab = int(spec.get("vocab", 0) or 0)
         if self.by_table and self.vocab < 1:
@@ -126,6 +136,8 @@ class MoE(FeedForward):
     def bind(self, tensors) -> None:
         super().bind(tensors)
         self._gate_pieces = None
+        if self.on_input:
+            self._ones = torch.ones(self.env.max_step_tokens * self.top_k, dtype=torch.float32, device=self.env.device)
         if self.env.dtype == torch.bfloat16 and SPLIT_ROUTER_PRODUCT and not self.by_table:
             self._gate_pieces = split_in_three(self.params["gate.weight"])
 
@@ -184,7 +196,7 @@ class MoE(FeedForward):
         routes = ws.get("moe.routes", (R,), torch.int32, (cap * k,))
         pos = ws.get("moe.pos", (R,), torch.int32, (cap * k,))
         bias = self.params.get("e_score_correction_bias")
-        if (dt == torch.bfloat16 and ops.moe_small_fits(T, self.hidden, self.inter, k)
+        if (dt == torch.bfloat16 and not self.on_input and ops.moe_small_fits(T, self.hidden, self.inter, k)
                 and (self.by_table or ops.moe_route_fits(T, self.hidden, E, k))):
             return self._few_tokens(h, h_f32, step, logits, ids, wts, bias)
         if self.by_table:  # the table names the experts; the sort is the one every router's choice gets
@@ -207,7 +219,12 @@ class MoE(FeedForward):
         if record is not None:  # measurement hook: which experts a step touched, layer by layer
             record.append(counts.clone())
         a = ws.get("moe.act", (R, self.inter), dt, (cap * k, self.inter))
-        if ops.moe_gemm1_gather_fits(dt, self.hidden, self.inter, E, R) and h.is_contiguous():
+        if self.on_input:  # rows scaled by their route's weight on the way into expert order
+            x = ws.get("moe.x", (R, self.hidden), dt, (cap * k, self.hidden))
+            ops.moe_gather_scaled(h, routes, wts.view(-1), k, x)
+            ops.moe_gemm1_act(x, self.params["experts.gate_up_proj"], offsets, self.act, self.alpha,
+                              self.limit, a)
+        elif ops.moe_gemm1_gather_fits(dt, self.hidden, self.inter, E, R) and h.is_contiguous():
             # the gate/up kernel reads each expert's rows where they lie: no copy into expert order
             ops.moe_gemm1_act_gather(h, routes, k, self.params["experts.gate_up_proj"], offsets, self.act,
                                      self.alpha, self.limit, a)
@@ -217,7 +234,8 @@ class MoE(FeedForward):
             ops.moe_gemm1_act(x, self.params["experts.gate_up_proj"], offsets, self.act, self.alpha,
                               self.limit, a)
         y = ws.get("moe.y", (R, self.hidden), dt, (cap * k, self.hidden))
-        ops.moe_gemm2(a, self.params["experts.down_proj"], offsets, routes, wts.view(-1), y)
+        ops.moe_gemm2(a, self.params["experts.down_proj"], offsets, routes,
+                      self._ones[:R] if self.on_input else wts.view(-1), y)
         shared = self.shared.forward(h, step) if self.shared is not None else None
         out = ws.get("moe.out", (T, self.hidden), dt, (cap, self.hidden))
         return RouteSum(y, pos, k, shared, T, out)

@@ -22,7 +22,8 @@ from .base import NORMS, BuildEnv, Norm, NormedSum, RouteSum, StreamSum
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``, ``gemma`` (bool: multiply by ``1 + w``)."""
+    """params: ``size``, ``eps``, ``gemma`` (bool: multiply by ``1 + w``), ``scalar`` (bool: the weight is one
+    number for all coordinates; the checkpoint tensor has no axis)."""
 
     takes_route_sum = True
     takes_normed_sum = True
@@ -32,10 +33,18 @@ class RMSNorm(Norm):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.gemma = bool(spec.get("gemma", True))
+        self.scalar = bool(spec.get("scalar", False))
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         init = ("normal", 0.0, 0.02) if self.gemma else ("normal", 1.0, 0.02)
-        return {"weight": ParamSpec((self.size,), "float32", init, store="bfloat16")}
+        if self.scalar and self.spec.get("init_std") is not None:
+            init = (init[0], init[1], float(self.spec["init_std"]))
+        return {"weight": ParamSpec(() if self.scalar else (self.size,), "float32", init, store="bfloat16")}
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.scalar:  # the kernels take one weight per coordinate
+            self.params["weight"] = self.params["weight"].reshape(1).expand(self.size).contiguous()
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         ops.add_rmsnorm(x, None, self.params["weight"], self.eps, self.gemma, out)

@@ -9,6 +9,9 @@ sequence rather than the checkpoint's ``max_position_embeddings``.  Mixers rotat
 their own kernels (``norm_rope_store``); one table serves all layers with equal parameters
 (``get_rope`` is cached the same way, rotary.py:211-231).
 
+``rope_interleaved``: the same angles and table; the pairs that turn together are the neighbours ``(2i, 2i + 1)``
+instead of ``(i, i + rotary_dim / 2)``.  A mixer's kernel asks the part (``interleaved``) which pairing to use.
+
 ``none``: no position encoding (a mixer that needs none asks for this kind).
 
 ``log_temperature``: no rotation; the table holds one factor per position,
@@ -32,6 +35,8 @@ from .base import POSITIONS, BuildEnv, PositionEncoding
 class NeoxRope(PositionEncoding):
     """params: ``rotary_dim`` (even, <= head_dim; 0 disables), ``theta``, ``precise`` (False: the reference's
     float32 operations; True: angles, cosines and sines in float64, rounded to float32 once)."""
+
+    interleaved = False
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         super().__init__(spec, env)
@@ -57,6 +62,13 @@ class NeoxRope(PositionEncoding):
             freqs = torch.einsum("i,j -> ij", t, inv_freq)
             self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(self.env.device)
         return self._table
+
+
+@POSITIONS.register("rope_interleaved")
+class InterleavedRope(NeoxRope):
+    """params: as ``rope_neox``.  Dimension ``2i`` turns with dimension ``2i + 1`` by ``position * theta^(-2i / rotary_dim)``."""
+
+    interleaved = True
 
 
 @POSITIONS.register("log_temperature")

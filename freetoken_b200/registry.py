@@ -38,6 +38,7 @@ _LAZY: Dict[str, str] = {
     "MiniMaxM3SparseForConditionalGeneration": "freetoken_b200.models.minimax_m3",
     "Rumalorn": "freetoken_b200.models.rumalorn",
     "Pabavik": "freetoken_b200.models.pabavik",
+    "Kekopel": "freetoken_b200.models.kekopel",
 }
 
 

@@ -31,7 +31,8 @@ class FusionRule:
 
     ``how``: ``"cat0"`` concatenates along dim 0; ``"stack"`` stacks ``[n, ...]``;
     ``"stack_pairs"`` takes sources two by two (gate, up), concatenates each pair along dim 0
-    and stacks the results (``[E, 2I, H]`` from ``w1``/``w3`` per expert)."""
+    and stacks the results (``[E, 2I, H]`` from ``w1``/``w3`` per expert); ``"same"`` is a plain rename of one
+    source of any shape (also a single number)."""
 
     target: str
     sources: List[str]
@@ -146,7 +147,10 @@ def _check_fusion(rule: FusionRule, ps: ParamSpec, shapes: Dict[str, Tuple[int, 
     want = tuple(ps.shape)
     srcs = rule.sources
     errs: List[str] = []
-    if rule.how == "cat0":
+    if rule.how == "same":
+        if len(srcs) != 1 or shapes[srcs[0]] != want:
+            errs.append(f"{rule.target}: file has {[list(shapes[s]) for s in srcs]}, model expects {list(want)}")
+    elif rule.how == "cat0":
         rows = sum(shapes[s][0] if shapes[s] else 0 for s in srcs)
         tails = {shapes[s][1:] for s in srcs}
         if rows != want[0] or tails != {want[1:]}:
@@ -173,7 +177,9 @@ def _check_fusion(rule: FusionRule, ps: ParamSpec, shapes: Dict[str, Tuple[int, 
 
 
 def _fusion_indices(rule: FusionRule, shapes: Dict[str, Tuple[int, ...]]):
-    if rule.how == "cat0":
+    if rule.how == "same":
+        yield rule.sources[0], (Ellipsis,)
+    elif rule.how == "cat0":
         r = 0
         for s in rule.sources:
             n = shapes[s][0]
@@ -194,7 +200,9 @@ def unfuse(rule: FusionRule, tensor: torch.Tensor) -> Dict[str, torch.Tensor]:
     """Inverse of a fusion, for writing checkpoints with per-part names."""
     out: Dict[str, torch.Tensor] = {}
     n = len(rule.sources)
-    if rule.how == "cat0":
+    if rule.how == "same":
+        out[rule.sources[0]] = tensor
+    elif rule.how == "cat0":
         sizes = list(rule.sizes) if rule.sizes is not None else [tensor.shape[0] // n] * n
         r = 0
         for s, k in zip(rule.sources, sizes):

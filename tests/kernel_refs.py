@@ -138,10 +138,11 @@ def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_i
                     s = s + dist_bias.float()[:, dist].view(Hkv, G, -1)
                 if sink is None:
                     p = torch.softmax(s, dim=-1)
-                else:  # a key without a value: it only takes its share of the weights
-                    top = torch.clamp(s.max(dim=-1, keepdim=True).values, min=float(sink))
+                else:  # a key without a value: it only takes its share of the weights (one logit, or one per head)
+                    sk = sink.float().view(Hkv, G, 1) if isinstance(sink, torch.Tensor) else torch.full((1, 1, 1), float(sink))
+                    top = torch.maximum(s.max(dim=-1, keepdim=True).values, sk)
                     e = torch.exp(s - top)
-                    p = e / (e.sum(-1, keepdim=True) + torch.exp(float(sink) - top))
+                    p = e / (e.sum(-1, keepdim=True) + torch.exp(sk - top))
                 o = torch.einsum("hgk,khd->hgd", p, vv)
             else:
                 o = torch.zeros(Hkv, G, D, device=q.device)
@@ -198,6 +199,12 @@ def router_topk(logits, bias, top_k, scoring, scale, ids, weights, n_parts=1):
         idx = torch.argsort(l, dim=-1, descending=True, stable=True)[:, :top_k]
         ids.copy_(idx.to(torch.int32))
         weights.copy_(torch.softmax(l.gather(-1, idx), dim=-1) * scale)
+        return
+    if scoring == "sigmoid_raw":  # the chosen experts' sigmoid scores as they are
+        sg = torch.sigmoid(l)
+        idx = torch.argsort(sg, dim=-1, descending=True, stable=True)[:, :top_k]
+        ids.copy_(idx.to(torch.int32))
+        weights.copy_(sg.gather(-1, idx) * scale)
         return
     s = torch.sigmoid(l) if scoring == "sigmoid" else torch.softmax(l, dim=-1)
     c = s + bias.float() if bias is not None else s
@@ -422,7 +429,120 @@ def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, seg_info, n_s
         state[slot] = S
 
 
-ALL = ["linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+def short_conv(x, w, state, state_slots, seg_info, n_segs, out):
+    """Per request: the step's inputs behind the slot's last ones; every output is its input plus the taps' sum."""
+    taps = w.shape[1]
+    keep = taps - 1
+    for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
+        slot = int(state_slots[i])
+        rows = x[q_start:q_start + q_len].float()
+        if keep:
+            old = torch.zeros(keep, x.shape[1]) if kv_len == q_len else state[slot].clone().float()
+            line = torch.cat([old, rows])
+        else:
+            line = rows
+        y = rows.clone()
+        for j in range(taps):
+            y = y + w[:, j].float() * line[j:j + q_len]
+        out[q_start:q_start + q_len] = y.to(out.dtype)
+        if keep:
+            state[slot] = line[-keep:]
+
+
+def depth_mix(hist, n_prev, mix, x):
+    T = x.shape[0]
+    hist[n_prev, :T] = x
+    acc = torch.zeros_like(x)
+    for j in range(n_prev + 1):
+        acc = acc + mix[j] * hist[j, :T]
+    x.copy_(acc)
+
+
+def moe_gather_scaled(h, sorted_routes, weights, top_k, out):
+    r = sorted_routes.long()
+    out.copy_((weights.float()[r][:, None] * h.float()[r // top_k]).to(out.dtype))
+
+
+def relu2_(x):
+    x.copy_((torch.relu(x.float()) ** 2).to(x.dtype))
+
+
+def _turn(v, pos, table, n_rot, interleaved):
+    """``v [..., dim]`` at position ``pos``: the first ``n_rot`` columns turn, by the table's row ``cos || sin``."""
+    if not n_rot:
+        return v
+    half = n_rot // 2
+    c, s = table[pos, :half].float(), table[pos, half:].float()
+    out = v.clone()
+    a = v[..., 0:n_rot:2] if interleaved else v[..., :half]
+    b = v[..., 1:n_rot:2] if interleaved else v[..., half:n_rot]
+    if interleaved:
+        out[..., 0:n_rot:2], out[..., 1:n_rot:2] = a * c - b * s, b * c + a * s
+    else:
+        out[..., :half], out[..., half:n_rot] = a * c - b * s, b * c + a * s
+    return out
+
+
+def latent_store(proj, q_rank, kv_rank, rot_dim, n_rot, interleaved, wq, wkv, eps, positions, rope_table, cq_out, slab,
+                 slot_map):
+    p = proj.float()
+    a, c, kr = p[:, :q_rank], p[:, q_rank:q_rank + kv_rank], p[:, q_rank + kv_rank:]
+    cq_out.copy_((a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps) * wq.float()).to(cq_out.dtype))
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * wkv.float()
+    flat = slab.view(-1, slab.shape[3])
+    for t in range(p.shape[0]):
+        slot = int(slot_map[t])
+        if slot < 0:
+            continue
+        row = torch.zeros(slab.shape[3])
+        row[:kv_rank] = c[t]
+        row[kv_rank:kv_rank + rot_dim] = _turn(kr[t], int(positions[t]), rope_table, n_rot, interleaved)
+        flat[slot] = row.to(slab.dtype)
+
+
+def latent_query_rotate(q, flat_dim, rot_dim, n_rot, interleaved, positions, rope_table, q_out, kv_rank):
+    for t in range(q.shape[0]):
+        q_out[t, :, kv_rank:] = 0
+        q_out[t, :, kv_rank:kv_rank + rot_dim] = _turn(q[t, :, flat_dim:].float(), int(positions[t]), rope_table, n_rot,
+                                                       interleaved).to(q_out.dtype)
+
+
+def mlstm_gates(pre, bias_i, bias_f, cap, m_state, state_slots, seg_info, n_segs, gate_i, logit_f, m_out):
+    H = pre.shape[1] // 2
+    gi = cap * torch.tanh((pre[:, :H].float() + bias_i.float()) / cap)
+    zf = cap * torch.tanh((pre[:, H:].float() + bias_f.float()) / cap)
+    gate_i.copy_(gi)
+    logit_f.copy_(zf)
+    f = torch.nn.functional.logsigmoid(zf)
+    for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
+        slot = int(state_slots[i])
+        m = torch.zeros(H) if kv_len == q_len else m_state[slot].clone()
+        for t in range(q_start, q_start + q_len):
+            m = torch.maximum(f[t] + m, gi[t])
+            m_out[t] = m
+        m_state[slot] = m
+
+
+def mlstm_prepare(proj, n_heads, dim, vdim, gate_i, logit_f, q32, k32, v32, z):
+    T, H = proj.shape[0], n_heads
+    p = proj.float()
+    q32.copy_(p[:, :H * dim])
+    k32.copy_((torch.exp(gate_i)[:, :, None] * p[:, H * dim:2 * H * dim].view(T, H, dim)).view(T, -1))
+    v = p[:, 2 * H * dim:2 * H * dim + H * vdim].view(T, H, vdim)
+    v32.copy_(torch.cat([v, torch.ones(T, H, 1)], dim=-1).view(T, -1))
+    z.copy_(logit_f[:, :, None].expand(T, H, dim).reshape(T, -1))
+
+
+def mlstm_output(o32, m, gates, norm_weight, eps, out):
+    T, H, dv1 = o32.shape
+    Dv = dv1 - 1
+    o = o32[:, :, :Dv] / (torch.clamp(o32[:, :, Dv:].abs(), min=1.0) + 1e-6 * torch.exp(m)[:, :, None])
+    o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)
+    y = o.reshape(T, H * Dv) * norm_weight.float() * torch.sigmoid(gates.float())
+    out.copy_(y.to(out.dtype))
+
+
+ALL = ["short_conv", "depth_mix", "moe_gather_scaled", "relu2_", "latent_store", "latent_query_rotate", "mlstm_gates", "mlstm_prepare", "mlstm_output", "linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gemm1_gather_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
