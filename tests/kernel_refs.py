@@ -139,7 +139,7 @@ def paged_attention(q, k_slab, v_slab, block_table, seg_info, n_segs, items, n_i
                 if sink is None:
                     p = torch.softmax(s, dim=-1)
                 else:  # a key without a value: it only takes its share of the weights (one logit, or one per head)
-                    sk = sink.float().view(Hkv, G, 1) if isinstance(sink, torch.Tensor) else torch.full((1, 1, 1), float(sink))
+                    sk = sink.float().view(Hkv, G, 1) if isinstance(sink, torch.Tensor) else torch.full((1, 1, 1), float(sink), device=q.device)
                     top = torch.maximum(s.max(dim=-1, keepdim=True).values, sk)
                     e = torch.exp(s - top)
                     p = e / (e.sum(-1, keepdim=True) + torch.exp(sk - top))

@@ -188,6 +188,7 @@ class PlainKekopel:
     def __init__(self, folder: str, dtype: torch.dtype = torch.float64):
         self.cfg, self.weights = load(folder, dtype)
         self.dtype = dtype
+        self.vocab = int(self.cfg["vocab"])
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:
         return forward(self.cfg, self.weights, tokens).float()

@@ -6,6 +6,8 @@ K2: one head; a window of 1 (a token sees itself only) and none at all; 2 taps; 
     (3 of 3); a layer without feed-forward; matrix memory with more key channels than values.
 K3: nothing is a multiple of 4: width 90, vocabulary 101, heads of 10 / 6, latents of 18 / 22, feed-forwards of 30 / 18;
     5 taps; 8 heads on the one cached row; matrix memory first, so that the stack starts with a recurrent layer.
+K5: sharp attention (a large score scale), so that a window one token off or a sink left out moves the logits by
+    far more than rounding: windows of 16 (a page's size) and 17, sizes whose cached row is 128 wide.
 K4: one tap (no convolution at all), matrix-memory layers only besides one attention layer with 32 heads (more
     than the 32-bit attention tile has rows), top 1.
 """
@@ -70,4 +72,9 @@ KEKO_4 = _model(120, 64, 1e-6, 1, [
     _layer("mlstm", _mem(4, 16, 16, 10.0), _dense(32)),
 ])
 
-ALL = {"K1": KEKO_1, "K2": KEKO_2, "K3": KEKO_3, "K4": KEKO_4}
+KEKO_5 = _model(96, 64, 1e-6, 4, [
+    _layer("latent_attention", _att(4, 32, 32, 32, 48, 96, 1.5, 16, 32, 10000.0), _dense(64)),
+    _layer("latent_attention", _att(2, 16, 32, 24, 32, 96, 2.0, 17, 32, 10000.0), _moe(32, 4, 2)),
+])
+
+ALL = {"K1": KEKO_1, "K2": KEKO_2, "K3": KEKO_3, "K4": KEKO_4, "K5": KEKO_5}
