@@ -1001,9 +1001,10 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
               "paged_attention_tc: tiles of 16 rows take at most 16 heads per KV head, got %d", n_q_heads / n_kv_heads);
   FTK_REQUIRE(n_tokens >= 1 && n_items >= 0 && n_segs >= 1 && num_pages >= 1 && bt_stride >= 1,
               "paged_attention_tc: bad sizes");
-  FTK_REQUIRE(window == 0 || (form == kTcSingle && k_slab != v_slab && !(extras && extras->dist_bias)),
-              "paged_attention_tc: of the tcgen05 kernels the one with 128-row tiles takes a window (values of their own, no "
-              "distance bias)");
+  // (one slab for keys and values: the rows zeroed before a window's first key lie in the key stage itself, which the
+  // score product of that tile has read by then)
+  FTK_REQUIRE(window == 0 || (form == kTcSingle && !(extras && extras->dist_bias)),
+              "paged_attention_tc: of the tcgen05 kernels the one with 128-row tiles takes a window (no distance bias)");
   FTK_REQUIRE(n_slots == 0 || (part_o && part_ml), "paged_attention_tc: split tiles need scratch");
   FTK_REQUIRE((((uintptr_t)q | (uintptr_t)k_slab | (uintptr_t)v_slab | (uintptr_t)out) & 15) == 0,
               "paged_attention_tc: 16-byte aligned tensors only");

@@ -459,7 +459,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     ``sink`` (a logit, a float32 tensor ``[Hq]`` of one logit per query head, or None): the softmax's denominator
     also holds ``e^sink``, a key without a value, so a row's weights are ``e^(s_j) / (e^sink + sum_i e^(s_i))``.  A tile that is split along the keys gets it once,
     in the merge.  Not with block selection.  Of the tcgen05 kernels the one with 128-row tiles takes a window and a
-    sink (its work list then starts every piece on a key tile: ``build_plan(..., window, key_tile=128)``).
+    sink (its work list then starts every piece on a key tile: ``build_plan(..., window, key_tile=128)``), also with
+    one slab for keys and values.
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -487,9 +488,9 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         if sel is not None or q.dtype != torch.bfloat16:
             raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without block selection")
         if window or sink is not None:  # the form with one 128-row query tile a piece takes both
-            if tile_rows != 128 or few_rows or dist_bias is not None or (window and v_slab.data_ptr() == k_slab.data_ptr()):
+            if tile_rows != 128 or few_rows or dist_bias is not None:
                 raise KernelError("paged_attention: of the tcgen05 kernels the one with 128-row tiles takes a window or a "
-                                  "sink (values of their own, no distance bias)")
+                                  "sink (no distance bias)")
             ex = _AttnExtras(None, 0, 1, 0 if sink is None else 1, 0.0 if sink is None else float(sink), sink_heads)
             _check(_lib().ftk_paged_attention_tc_ex(
                 _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),

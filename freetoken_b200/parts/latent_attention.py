@@ -113,9 +113,11 @@ class LatentAttention(Mixer):
 
     # ------------------------------------------------------------------ step
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
-        # (keys that are the values, a window and a sink together: the tiles of 16 / 64 rows take them)
-        return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens, 0, page_size,
-                                     self.window, longest_span, one_tile_only=True, no_few=True)
+        # (keys that are the values, a window and a sink together: the tiles of 16 / 64 rows take them, and of the
+        # tcgen05 kernels the one with a single 128-row tile a piece, whose head is 128 wide)
+        sized = self.kv_split == 1
+        return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens, self.pad_dim if sized else 0,
+                                     page_size, self.window, longest_span, one_tile_only=True, no_few=True)
 
     def plan_key(self, decode_only: bool = False, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
         rows, few = self.kernel_form(decode_only, n_tokens, page_size, longest_span)

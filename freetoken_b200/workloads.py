@@ -14,12 +14,14 @@ time of a step at the start and at the end of the prompt.
 
 ``designs``: Rumalorn (parallel Dynamic-Tanh layers, key-tied attention with a bias by distance, experts
 named by a table over token ids) and Pabavik (layers normed on both sides of every sub-layer; windowed attention
-with a sink and an output gate, gated linear attention and attention over an earlier layer's cache in turns)
+with a sink and an output gate, gated linear attention and attention over an earlier layer's cache in turns) and
+Kekopel (a short convolution in front of every sub-layer, norms behind them, a mix over all layers' outputs; latent
+attention with a learned sink per head and matrix memory in turns; dense and input-weighted expert feed-forwards)
 beside MiniMax-M3 at equal layer sizes, all with random weights: a
 2 048-token prompt in one step and decode steps of eight requests at 2 048 tokens of context, at a few
 sizes that resemble real models' layers.
 
-    python bench.py --workload designs [--layers 4]
+    python bench.py --workload designs [--layers 4] [--designs kekopel,pabavik]
 
 Each prints one JSON line.  The reference times whole generations of this kind in
 benchmarks/bench_decode_moe.py:8-24 (tokens after the first / time between first and last).
@@ -29,7 +31,7 @@ from __future__ import annotations
 
 import json
 import time
-from typing import Any, Dict
+from typing import Any, Dict, Optional
 
 import numpy as np
 import torch
@@ -164,7 +166,19 @@ def _design_configs(width, heads, kv, dim, experts, top, ff, vocab, layers):
             players.append({"type": "attention", "mixer": dict(att, kv_from=i - 2), "mlp": pmlp})
     paba = {"architecture": "Pabavik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
             "logit_softcap": 30.0, "layers": players}
-    return {"rumalorn": ruma, "pabavik": paba, "minimax_m3": m3}
+    # Kekopel: latent attention (one cached row of kv_rank + rot_dim per token under all heads, the same window)
+    # and matrix memory in turns (two to one), dense and expert feed-forwards in turns, a short convolution in front of
+    # every sub-layer and the mix over all layers' outputs behind every layer
+    # (a cached row of 128 at the two smaller sizes, which the tcgen05 attention kernel takes, of 256 at the largest)
+    rank, rot = (96, 32) if width <= 2048 else (192, 64)
+    lat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "q_rank": width // 2, "kv_rank": rank,
+           "scale": (dim + rot) ** -0.5, "mask": {"size": window}, "rot": {"dims": rot, "base": 500000.0}}
+    mem = {"heads": heads, "dim": dim, "vdim": dim, "gate_cap": 15.0}
+    kmlp = [{"kind": "dense", "ff": top * ff}, {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}]
+    keko = {"architecture": "Kekopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "layers": [{"type": "mlstm" if i % 3 == 2 else "latent_attention", "mixer": dict(mem if i % 3 == 2 else lat),
+                        "mlp": kmlp[i % 2]} for i in range(layers)]}
+    return {"rumalorn": ruma, "pabavik": paba, "kekopel": keko, "minimax_m3": m3}
 
 
 def _time_design(raw: Dict[str, Any], prompt: int, batch: int, steps: int, warmup: int) -> Dict[str, Any]:
@@ -215,8 +229,9 @@ def _time_design(raw: Dict[str, Any], prompt: int, batch: int, steps: int, warmu
 
 
 def designs(raw: Dict[str, Any], layers: int = 4, prompt: int = 2048, batch: int = 8, steps: int = 32,
-            warmup: int = 8) -> Dict[str, Any]:
-    """``raw`` (the headline configuration) is not used: the sizes are this workload's own."""
+            warmup: int = 8, only: Optional[str] = None) -> Dict[str, Any]:
+    """``raw`` (the headline configuration) is not used: the sizes are this workload's own.  ``only``: designs to time,
+    with commas between them (MiniMax-M3 is always timed)."""
     import gc
 
     out: Dict[str, Any] = {"workload": "designs", "layers": layers, "prompt": prompt, "decode_batch": batch,
@@ -226,11 +241,16 @@ def designs(raw: Dict[str, Any], layers: int = 4, prompt: int = 2048, batch: int
         width, heads, kv, dim, experts, top, ff, vocab = dims
         row: Dict[str, Any] = {"width": width, "q_heads": heads, "kv_heads": kv, "head_dim": dim, "experts": experts,
                                "top_k": top, "expert_width": ff, "vocab": vocab}
+        chosen = set(only.split(",")) | {"minimax_m3"} if only else None
         for design, cfg in _design_configs(*dims, layers).items():
+            if chosen is not None and design not in chosen:
+                continue
             row[design] = _time_design(cfg, prompt, batch, steps, warmup)
             gc.collect()
             torch.cuda.empty_cache()
-        for design in ("rumalorn", "pabavik"):
+        for design in ("rumalorn", "pabavik", "kekopel"):
+            if design not in row:
+                continue
             row[f"{design}_over_minimax_m3"] = {
                 "prefill": round(row[design]["prefill_tokens_per_s"] / row["minimax_m3"]["prefill_tokens_per_s"], 3),
                 "decode": round(row[design]["decode_tokens_per_s"] / row["minimax_m3"]["decode_tokens_per_s"], 3)}

@@ -15,7 +15,8 @@ import kernel_refs as ref
 from freetoken_b200.engine.engine import StepEntry
 from helpers import make_engine, mixed_schedule, model_folder, replay_cuts, replay_mixed, replay_whole, tokens_for
 from plain.kekopel_plain import PlainKekopel
-from test_pabavik_gpu import assert_rows
+from test_pabavik_gpu import assert_rows, attention_problem, attn_tol
+from test_pabavik_gpu import run_attention as run_attention_case
 from tiny_kekopel import ALL, KEKO_1, PAGE
 
 from freetoken_b200.engine.attention_plan import build_plan
@@ -262,6 +263,27 @@ def test_a_key_at_the_windows_edge(dtype, window, q_len):
                 assert hit < 1.0, (window, q_len, which, hit)
 
 
+@pytest.mark.parametrize("Hq,P,window", [(4, 16, 96), (16, 16, 200), (8, 32, 37), (48, 16, 128), (2, 64, 1), (128, 16, 1000)])
+def test_one_slab_with_window_and_sinks_on_the_tensor_core_kernel(Hq, P, window):
+    """The tcgen05 kernel with 128-row tiles on cached rows that are key and value at once: pieces that start on a
+    key tile before the window's first key, pages before the window that hold NaN (they may have gone back to the
+    pool), tiles split along the keys, one sink per head."""
+    dtype = torch.bfloat16
+    sink = rnd(Hq, seed=8, scale=1.5)
+    for segs_, force in (([(300, 300)], False), ([(128, 128), (1, 40), (200, 517), (3, 3)], False), ([(256, 900)], True),
+                         ([(130, 1000)], False)):
+        q, ks, _, bt, seg = attention_problem(dtype, Hq, 1, 128, P, segs_, seed=6)
+        for q_start, q_len, kv_len, row in seg.tolist():
+            for j in range(0, max(0, kv_len - q_len - window + 1)):
+                ks[int(bt[row, j // P]), :, j % P] = float("nan")
+        ops.variant_counts(reset=True)
+        out, want, plan = run_attention_case(dtype, Hq, 1, 128, P, segs_, 128, window, sink, force_split=force,
+                                             problem=(q, ks, ks, bt, seg))
+        assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, window or sink", 0) == 1
+        torch.testing.assert_close(out.float(), want.float(), **attn_tol(dtype))
+    assert ops.read_status() == 0
+
+
 # --------------------------------------------------------------------------- matrix memory
 def plain_memory(q, k, v, gi, f, m0, S0, n0):
     """The recurrence as the design states it, with the running maximum, from a given state."""
@@ -428,6 +450,26 @@ def test_long_prompt_long_decoding_and_recorded_steps(name, dtype, tmp_path_fact
         got.append(eng.step([StepEntry("a", toks[i:i + 1], [0])]).logits.float().cpu().clone())
     assert_rows(long, plain.logits(other), dtype, "the long step", plain.router_gaps(other) * SHARP.get(name, 1.0))
     assert_rows(torch.cat(got), want[:40], dtype, "decode steps before and after it", gaps)
+    eng.check_kernels()
+
+
+def test_long_steps_of_rows_of_128_run_the_tensor_core_attention(tmp_path_factory):
+    folder = model_folder(tmp_path_factory.getbasetemp(), "K5", ALL["K5"])
+    plain = PlainKekopel(folder)
+    toks = tokens_for(plain.vocab, 300, 9)
+    want, gaps = plain.logits(toks), plain.router_gaps(toks) * SHARP["K5"]
+    eng = make_engine(folder, "bfloat16", DEV, 16, pages=96, max_step=512)
+    ops.variant_counts(reset=True)
+    assert_rows(replay_whole(eng, "w", toks), want, "bfloat16", "whole", gaps)
+    assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, window or sink", 0) == 2
+    assert_rows(replay_cuts(eng, "c", toks, [150, 130, 2]), want, "bfloat16", "portions, the rest one by one", gaps)
+    others = {f"o{i}": tokens_for(plain.vocab, 20 + i, 20 + i) for i in range(3)}
+    for r, t in others.items():  # three requests that decode beside a long portion
+        eng.step([StepEntry(r, t[:-1], [])])
+    out = eng.step([StepEntry("long", toks[:200], list(range(200)))] + [StepEntry(r, t[-1:], [0]) for r, t in others.items()])
+    assert_rows(out.logits[:200], want[:200], "bfloat16", "a long portion beside single tokens", gaps)
+    for i, (r, t) in enumerate(others.items()):
+        assert_rows(out.logits[200 + i:201 + i], plain.logits(t)[-1:], "bfloat16", r)
     eng.check_kernels()
 
 
