@@ -16,7 +16,9 @@ constexpr int kConvTile = 16;     // tokens per tile (at least taps - 1)
 constexpr int kConvMaxTaps = 16;
 constexpr int kConvThreads = 128; // four channels a thread
 
-template <typename T>
+// TAPS > 0: the tap count at compile time.  A thread then keeps its channels' last TAPS - 1 inputs in registers and
+// fetches every row of the stream once; TAPS == 0 takes any count and fetches a row once per tap (from L1).
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(kConvThreads)
 short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, int taps, float* __restrict__ state,
                   const int32_t* __restrict__ state_slots, const int32_t* __restrict__ seg_info, int n_segs, int n_slots,
@@ -36,22 +38,63 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, int 
   if (c0 >= C) return;
   const int nc = min(4, C - c0);
   const bool vec = nc == 4 && (C & 3) == 0;
+  if (TAPS > 0) taps = TAPS;
   const int keep = taps - 1;
   const int slot = state_slots[seg];
   const bool has_slot = slot >= 0 && slot < n_slots;
   const int before = kv_len - q_len;                       // tokens the request held before this step
   float* st = has_slot ? state + ((size_t)slot * keep) * C + c0 : nullptr;  // row i: the input `keep - i` places back
-  float wt[kConvMaxTaps][4];
-  for (int j = 0; j < taps; ++j)
+  constexpr int kMost = TAPS > 0 ? TAPS : kConvMaxTaps;
+  float wt[kMost][4];
+#pragma unroll
+  for (int j = 0; j < (TAPS > 0 ? TAPS : taps); ++j)
+#pragma unroll
     for (int i = 0; i < 4; ++i) wt[j][i] = i < nc ? w[(size_t)(c0 + i) * taps + j] : 0.f;
-  float old[kConvMaxTaps][4];                              // the slot's rows, read by tile 0 only
+  float old[kMost][4];                                     // the slot's rows, read by tile 0 only
   const bool first = tile == 0;
   if (first) {
-    for (int r = 0; r < keep; ++r)
+#pragma unroll
+    for (int r = 0; r < (TAPS > 0 ? TAPS - 1 : keep); ++r)
+#pragma unroll
       for (int i = 0; i < 4; ++i)
         old[r][i] = (st && before > 0 && i < nc && keep - r <= before) ? st[(size_t)r * C + i] : 0.f;
   }
   const int t0 = tile * kConvTile, t1 = min(q_len, t0 + kConvTile);
+  if (TAPS > 1 && vec) {
+    constexpr int K = TAPS > 1 ? TAPS - 1 : 1;
+    float win[K][4];                                       // inputs t - K .. t - 1, oldest first
+#pragma unroll
+    for (int r = 0; r < K; ++r) {
+      if (first) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) win[r][i] = old[r][i];
+      } else {
+        Vec4<float>::load(x + (size_t)(q_start + t0 - K + r) * C + c0, win[r]);
+      }
+    }
+    const float* row = x + (size_t)(q_start + t0) * C + c0;
+    T* o = out + (size_t)(q_start + t0) * C + c0;
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t, row += C, o += C) {
+      float cur[4], acc[4];
+      Vec4<float>::load(row, cur);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = cur[i];        // the same order of sums as the form for any count
+#pragma unroll
+      for (int r = 0; r < K; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fmaf(wt[r][i], win[r][i], acc[i]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(wt[K][i], cur[i], acc[i]);
+      Vec4<T>::store(o, acc);
+#pragma unroll
+      for (int r = 0; r + 1 < K; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) win[r][i] = win[r + 1][i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) win[K - 1][i] = cur[i];
+    }
+  } else
   for (int t = t0; t < t1; ++t) {
     float acc[4];
     const float* row = x + (size_t)(q_start + t) * C + c0;
@@ -131,6 +174,16 @@ __global__ void moe_gather_scaled_kernel(const T* __restrict__ h, const int32_t*
   const float wgt = weights[route];
   const T* src = h + (size_t)t * hidden;
   T* dst = out + (size_t)r * hidden;
+  if ((hidden & 3) == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float v[4];
+      Vec4<T>::load(src + i, v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] *= wgt;
+      Vec4<T>::store(dst + i, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<T>(wgt * to_float(src[i]));
 }
 
@@ -139,10 +192,23 @@ template <typename T>
 __global__ void relu2_kernel(T* __restrict__ x, long long n) {
   pdl_wait();
   pdl_trigger();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
-  const float v = fmaxf(to_float(x[i]), 0.f);
-  x[i] = from_float<T>(v * v);
+  if (i + 4 <= n && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    float v[4];
+    Vec4<T>::load(x + i, v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[k] = fmaxf(v[k], 0.f);
+      v[k] *= v[k];
+    }
+    Vec4<T>::store(x + i, v);
+    return;
+  }
+  for (long long j = i; j < n && j < i + 4; ++j) {
+    const float v = fmaxf(to_float(x[j]), 0.f);
+    x[j] = from_float<T>(v * v);
+  }
 }
 
 }  // namespace ftk
@@ -162,12 +228,20 @@ extern "C" int ftk_short_conv(const float* x, const float* w, int taps, float* s
   // tiles: every request's tokens rounded up, so at most n_tokens / tile + n_segs
   dim3 grid((n_tokens + kConvTile - 1) / kConvTile + n_segs, (channels + kConvThreads * 4 - 1) / (kConvThreads * 4));
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == FTK_F32)
-    FTK_LAUNCH(short_conv_kernel<float>, grid, kConvThreads, 0, s, x, w, taps, state, state_slots, seg_info, n_segs, n_slots,
-               (float*)out, n_tokens, channels);
-  else
-    FTK_LAUNCH(short_conv_kernel<__nv_bfloat16>, grid, kConvThreads, 0, s, x, w, taps, state, state_slots, seg_info, n_segs,
-               n_slots, (__nv_bfloat16*)out, n_tokens, channels);
+#define FTK_CONV(TY, N)                                                                                              \
+  FTK_LAUNCH((short_conv_kernel<TY, N>), grid, kConvThreads, 0, s, x, w, taps, state, state_slots, seg_info, n_segs, \
+             n_slots, (TY*)out, n_tokens, channels)
+#define FTK_CONV_TAPS(TY)                  \
+  do {                                     \
+    if (taps == 2) FTK_CONV(TY, 2);        \
+    else if (taps == 3) FTK_CONV(TY, 3);   \
+    else if (taps == 4) FTK_CONV(TY, 4);   \
+    else FTK_CONV(TY, 0);                  \
+  } while (0)
+  if (dtype == FTK_F32) FTK_CONV_TAPS(float);
+  else FTK_CONV_TAPS(__nv_bfloat16);
+#undef FTK_CONV_TAPS
+#undef FTK_CONV
   FTK_LAUNCH_CHECK("short_conv");
   return 0;
 }
@@ -209,7 +283,7 @@ extern "C" int ftk_relu2(void* x, int dtype, long long n, void* stream) {
   if (n == 0) return 0;
   FTK_REQUIRE(x, "relu2: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  const unsigned blocks = (unsigned)((n + 255) / 256);
+  const unsigned blocks = (unsigned)(((n + 3) / 4 + 255) / 256);
   if (dtype == FTK_F32) FTK_LAUNCH(relu2_kernel<float>, blocks, 256, 0, s, (float*)x, n);
   else FTK_LAUNCH(relu2_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)x, n);
   FTK_LAUNCH_CHECK("relu2");

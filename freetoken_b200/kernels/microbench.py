@@ -12,6 +12,8 @@
     python -m freetoken_b200.kernels.microbench attention --prefill 2048 --window 1024 --sink
     python -m freetoken_b200.kernels.microbench gla --prefill 2048 [--heads 16 --dim 128 --vdim 128]
     python -m freetoken_b200.kernels.microbench gla --batch 8
+    python -m freetoken_b200.kernels.microbench kekopel --tokens 2048 [--batch 8]
+    python -m freetoken_b200.kernels.microbench attention --prefill 2048 --tied --kv-heads 1 --window 1024 --head-sinks
 
 Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
 times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
@@ -141,6 +143,8 @@ def bench_attention(a) -> dict:
     fixed = None
     window = int(getattr(a, "window", 0) or 0) or None  # a sliding window
     sink = 0.0 if getattr(a, "sink", False) else None  # a sink of logit 0 in the softmax's denominator
+    if getattr(a, "head_sinks", False):  # a logit per query head
+        sink = torch.randn(Hq, device=dev, generator=g)
     special = window is not None or sink is not None  # of the tcgen05 kernels the one with 128-row tiles takes these
     no_tc = a.no_tc
     tile = 128 if (a.prefill >= 128 and not no_tc and ops.attention_tc_fits(D, P, G)) else 64
@@ -278,6 +282,111 @@ def bench_gla(a) -> dict:
             "gbs": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / HBM_GBS, 3)}
 
 
+def bench_kekopel(a) -> dict:
+    """The kernels that the Kekopel layers add around the library products: the short convolution in front of a
+    sub-layer, the sub-layer's norm into the stream, the mix over all layers' outputs, the latent-attention rows
+    (norms, rotation, cache row; the queries' rotated part), the matrix memory's gates, inputs, recurrence (with the
+    normaliser as one more value column) and output, the squared ReLU and the scaled expert inputs.  Attention over
+    the latent rows is ``attention --tied --kv-heads 1 --window W --head-sinks``."""
+    from ..parts.gla import chunk_list
+
+    dev = "cuda"
+    T, C, H, D, taps, depth = a.tokens, a.hidden, a.heads, a.head_dim, a.taps, a.depth
+    decode = a.batch > 0
+    segs = [(1, a.context)] * a.batch if decode else [(T, T)]
+    T = sum(q for q, _ in segs)
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf, f32 = torch.bfloat16, torch.float32
+    info, q0 = [], 0
+    for ql, kv in segs:
+        info.append([q0, ql, kv, 0])
+        q0 += ql
+    seg = torch.tensor(info, dtype=torch.int32, device=dev)
+    slots = torch.arange(1, len(segs) + 1, dtype=torch.int32, device=dev)
+    n_slots = len(segs) + 1
+    results = {}
+
+    def add(name, fn, nbytes, flops=0):
+        us = _time(fn, a.iters, a.warmup, a.profile)
+        results[name] = {"us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1),
+                         "hbm_frac": round(nbytes / us / 1e3 / HBM_GBS, 3)}
+        if flops:
+            fp32_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+            results[name].update(flops=flops, tflops=round(flops / us / 1e6, 2),
+                                 fp32_frac_nominal=round(flops / us / 1e6 / fp32_tflops, 3))
+
+    res = torch.randn(T, C, device=dev, generator=g)
+    y = torch.randn(T, C, device=dev, generator=g).to(bf)
+    out = torch.empty(T, C, dtype=bf, device=dev)
+    cw = torch.randn(C, taps, device=dev, generator=g) * 0.3
+    cstate = torch.zeros(n_slots, max(taps - 1, 1), C, device=dev)[:, : taps - 1]
+    add("short_conv", lambda: ops.short_conv(res, cw, cstate if taps > 1 else None, slots, seg, len(segs), out),
+        T * C * (4 + 2) + (2 * len(segs) * (taps - 1) * C * 4 if decode else 0))
+    w = torch.ones(C, device=dev)
+    add("postnorm_add_norm (a sub-layer's norm into the stream)",
+        lambda: ops.postnorm_add_norm(y, None, w, 1e-6, False, res), T * C * (2 + 4 + 4))
+    hist = torch.randn(depth + 1, T, C, device=dev, generator=g)
+    mix = torch.rand(depth + 1, device=dev, generator=g)
+    add(f"depth_mix (over {depth + 1} outputs)", lambda: ops.depth_mix(hist, depth, mix, res), T * C * 4 * (depth + 3))
+    inter = a.inter
+    act = torch.randn(T, inter, device=dev, generator=g).to(bf)
+    add("relu2 (in place)", lambda: ops.relu2_(act), T * inter * 2 * 2)
+    k_top = a.top_k
+    routes = torch.randperm(T * k_top, device=dev, generator=g).to(torch.int32)
+    wts = torch.rand(T * k_top, device=dev, generator=g)
+    xin = torch.empty(T * k_top, C, dtype=bf, device=dev)
+    add("moe_gather_scaled", lambda: ops.moe_gather_scaled(y, routes, wts, k_top, xin), T * C * 2 + T * k_top * C * 2)
+    # latent attention
+    qr, kr, rot, P = a.q_rank, a.kv_rank, a.rot_dim, 16
+    pad = -(-(kr + rot) // 16) * 16
+    proj = torch.randn(T, qr + kr + rot, device=dev, generator=g).to(bf)
+    cq = torch.empty(T, qr, dtype=bf, device=dev)
+    slab = torch.zeros(-(-T // P) + 1, 1, P, pad, dtype=bf, device=dev)
+    slot_map = torch.arange(P, P + T, dtype=torch.int32, device=dev)
+    positions = torch.arange(T, dtype=torch.int32, device=dev) if not decode else \
+        torch.full((T,), a.context - 1, dtype=torch.int32, device=dev)
+    table = torch.randn(max(T, a.context), rot, device=dev, generator=g)
+    wq, wkv = torch.ones(qr, device=dev), torch.ones(kr, device=dev)
+    add("latent_store", lambda: ops.latent_store(proj, qr, kr, rot, rot, True, wq, wkv, 1e-6, positions, table, cq, slab,
+                                                 slot_map), T * ((qr + kr + rot) * 2 + qr * 2 + pad * 2))
+    q = torch.randn(T, H, D + rot, device=dev, generator=g).to(bf)
+    qa = torch.empty(T, H, pad, dtype=bf, device=dev)
+    add("latent_query_rotate", lambda: ops.latent_query_rotate(q, D, rot, rot, True, positions, table, qa, kr),
+        T * H * (rot * 2 + (pad - kr) * 2))
+    # matrix memory
+    Dv = a.vdim
+    pre = torch.randn(T, 2 * H, device=dev, generator=g)
+    bias = torch.randn(2 * H, device=dev, generator=g)
+    m_state = torch.zeros(n_slots, H, device=dev)
+    gi, zf, m = (torch.empty(T, H, device=dev) for _ in range(3))
+    add("mlstm_gates", lambda: ops.mlstm_gates(pre, bias[:H], bias[H:], 15.0, m_state, slots, seg, len(segs), gi, zf, m),
+        T * H * 4 * 5)
+    wide = (torch.randn(T, H * (2 * D + 2 * Dv), device=dev, generator=g) * 0.3).to(bf)
+    q32, k32, z = (torch.empty(T, H * D, device=dev) for _ in range(3))
+    v32 = torch.empty(T, H * (Dv + 1), device=dev)
+    add("mlstm_prepare", lambda: ops.mlstm_prepare(wide, H, D, Dv, gi, zf, q32, k32, v32, z),
+        T * H * ((2 * D + Dv) * 2 + (3 * D + Dv + 1) * 4))
+    chunks, per_seg, single, multi = chunk_list(segs, a.chunk)
+    n = chunks.shape[0]
+    state = torch.zeros(n_slots, H, D, Dv + 1, device=dev)
+    carry = torch.empty(n, H, D, Dv + 1, device=dev) if multi else None
+    decay = torch.empty(n, H, D, device=dev) if multi else None
+    o32 = torch.empty(T, H, Dv + 1, device=dev)
+    cd, pd = torch.from_numpy(chunks).to(dev), torch.from_numpy(per_seg).to(dev)
+    passes = 2 if multi else 1
+    add("gla_scan (32-bit inputs, the normaliser as one more value column)",
+        lambda: ops.gla_scan(q32, k32, v32, z, None, 1.0, D ** -0.5, state, slots, seg, len(segs), cd, n, pd, single, multi,
+                             carry, decay, o32),
+        T * H * (3 * D + Dv + 1) * 4 * passes + T * H * (Dv + 1) * 4 + (2 * len(segs) + (2 * n if multi else 0)) * H * D * (Dv + 1) * 4,
+        T * H * D * (Dv + 1) * (8 if multi else 5))
+    o = torch.empty(T, H * Dv, dtype=bf, device=dev)
+    nw = torch.ones(H * Dv, device=dev)
+    add("mlstm_output", lambda: ops.mlstm_output(o32, m, wide[:, H * (2 * D + Dv):], nw, 1e-6, o),
+        T * H * ((Dv + 1) * 4 + 4 + Dv * 2 * 2))
+    results["status"] = ops.read_status()
+    return results
+
+
 def bench_few(a) -> dict:
     """The few-token kernels (``csrc/gemv.cu``) at the headline sizes: the qkv and output projections of
     ``--tokens`` tokens, and the routed gate/up and down products of their routes.  Six copies of the dense
@@ -393,7 +502,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample", "sparse", "few", "rows", "gla"):
+    for name in ("moe", "attention", "sample", "sparse", "few", "rows", "gla", "kekopel"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -426,12 +535,29 @@ def main(argv=None) -> int:
             p.add_argument("--dist-bias", type=int, default=0, help="entries per head of a bias by distance (0 = none)")
             p.add_argument("--window", type=int, default=0, help="a sliding window of this many tokens (0 = none)")
             p.add_argument("--sink", action="store_true", help="a sink of logit 0 in the softmax's denominator")
+            p.add_argument("--head-sinks", action="store_true", help="a sink with a logit of its own per query head")
         elif name == "rows":
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--hidden", type=int, default=3072)
             p.add_argument("--q-heads", type=int, default=48)
             p.add_argument("--kv-heads", type=int, default=8)
             p.add_argument("--head-dim", type=int, default=128)
+        elif name == "kekopel":
+            p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--batch", type=int, default=0, help="requests with one token each instead of one portion")
+            p.add_argument("--context", type=int, default=2048)
+            p.add_argument("--hidden", type=int, default=3072)
+            p.add_argument("--inter", type=int, default=12288)
+            p.add_argument("--top-k", type=int, default=8)
+            p.add_argument("--heads", type=int, default=48)
+            p.add_argument("--head-dim", type=int, default=128)
+            p.add_argument("--vdim", type=int, default=128)
+            p.add_argument("--q-rank", type=int, default=1536)
+            p.add_argument("--kv-rank", type=int, default=192)
+            p.add_argument("--rot-dim", type=int, default=64)
+            p.add_argument("--taps", type=int, default=4)
+            p.add_argument("--depth", type=int, default=3, help="outputs before this layer's that the mix reads")
+            p.add_argument("--chunk", type=int, default=64)
         elif name == "few":
             p.add_argument("--tokens", type=int, default=1)
             p.add_argument("--hidden", type=int, default=3072)
@@ -469,7 +595,7 @@ def main(argv=None) -> int:
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
     res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse, "few": bench_few,
-           "rows": bench_rows, "gla": bench_gla}[a.case](a)
+           "rows": bench_rows, "gla": bench_gla, "kekopel": bench_kekopel}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

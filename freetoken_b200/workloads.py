@@ -170,7 +170,7 @@ def _design_configs(width, heads, kv, dim, experts, top, ff, vocab, layers):
     # and matrix memory in turns (two to one), dense and expert feed-forwards in turns, a short convolution in front of
     # every sub-layer and the mix over all layers' outputs behind every layer
     # (a cached row of 128 at the two smaller sizes, which the tcgen05 attention kernel takes, of 256 at the largest)
-    rank, rot = (96, 32) if width <= 2048 else (192, 64)
+    rank, rot = (64, 64) if width <= 2048 else (192, 64)
     lat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "q_rank": width // 2, "kv_rank": rank,
            "scale": (dim + rot) ** -0.5, "mask": {"size": window}, "rot": {"dims": rot, "base": 500000.0}}
     mem = {"heads": heads, "dim": dim, "vdim": dim, "gate_cap": 15.0}

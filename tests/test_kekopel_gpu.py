@@ -135,7 +135,7 @@ def test_router_keeps_the_raw_sigmoid_scores(E, k, T):
 
 # --------------------------------------------------------------------------- latent attention
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("Q,C,R,n_rot,inter,pad", [(96, 96, 32, 32, True, 128), (24, 40, 8, 4, True, 48), (18, 22, 6, 6, True, 32),
+@pytest.mark.parametrize("Q,C,R,n_rot,inter,pad", [(80, 112, 16, 16, True, 128), (24, 40, 8, 4, True, 48), (18, 22, 6, 6, True, 32),
                                                     (16, 24, 16, 16, False, 48), (12, 16, 8, 0, True, 32), (300, 200, 56, 56, True, 256)])
 def test_latent_rows_and_queries(dtype, Q, C, R, n_rot, inter, pad):
     T, H, D, P, pages = 11, 3, 10, 4, 9
@@ -202,7 +202,7 @@ def run_attention(q, slab, table, q_len, kv_len, dtype, window, sink, scale=1.0,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("Hq,D,P,window,split", [(4, 128, 16, 96, 1), (8, 32, 4, 13, 1), (32, 16, 4, 300, 2), (2, 48, 8, 17, 1), (1, 32, 16, 1, 1)])
+@pytest.mark.parametrize("Hq,D,P,window,split", [(6, 128, 16, 72, 1), (8, 32, 4, 13, 1), (32, 16, 4, 300, 2), (2, 48, 8, 17, 1), (1, 32, 16, 1, 1)])
 def test_one_cached_row_as_key_and_value_with_a_sink_per_head(dtype, Hq, D, P, window, split):
     L, q_len = 150, 40
     if dtype == torch.bfloat16 and split > 1:
@@ -234,7 +234,7 @@ def test_a_large_sink_silences_its_head_only(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window", [1, 7, 16, 17, 64, 65, 96])
+@pytest.mark.parametrize("window", [1, 7, 16, 17, 64, 65, 100])
 @pytest.mark.parametrize("q_len", [1, 33])
 def test_a_key_at_the_windows_edge(dtype, window, q_len):
     """Among 200 keys one matches the last query (its score stands out): just inside the window the output is that
@@ -263,7 +263,7 @@ def test_a_key_at_the_windows_edge(dtype, window, q_len):
                 assert hit < 1.0, (window, q_len, which, hit)
 
 
-@pytest.mark.parametrize("Hq,P,window", [(4, 16, 96), (16, 16, 200), (8, 32, 37), (48, 16, 128), (2, 64, 1), (128, 16, 1000)])
+@pytest.mark.parametrize("Hq,P,window", [(6, 16, 72), (16, 16, 200), (8, 32, 37), (48, 16, 128), (2, 64, 1), (128, 16, 1000)])
 def test_one_slab_with_window_and_sinks_on_the_tensor_core_kernel(Hq, P, window):
     """The tcgen05 kernel with 128-row tiles on cached rows that are key and value at once: pieces that start on a
     key tile before the window's first key, pages before the window that hold NaN (they may have gone back to the

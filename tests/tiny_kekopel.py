@@ -73,8 +73,8 @@ KEKO_4 = _model(120, 64, 1e-6, 1, [
 ])
 
 KEKO_5 = _model(96, 64, 1e-6, 4, [
-    _layer("latent_attention", _att(4, 32, 32, 32, 48, 96, 1.5, 16, 32, 10000.0), _dense(64)),
-    _layer("latent_attention", _att(2, 16, 32, 24, 32, 96, 2.0, 17, 32, 10000.0), _moe(32, 4, 2)),
+    _layer("latent_attention", _att(4, 32, 48, 32, 48, 80, 1.5, 16, 48, 10000.0), _dense(64)),
+    _layer("latent_attention", _att(2, 16, 16, 24, 32, 112, 2.0, 17, 16, 10000.0), _moe(32, 4, 2)),
 ])
 
 ALL = {"K1": KEKO_1, "K2": KEKO_2, "K3": KEKO_3, "K4": KEKO_4, "K5": KEKO_5}
