@@ -123,13 +123,15 @@ int ftk_gated_heads(const void* x, int x_f32, int x_stride, const void* gates, l
 // within the segment, tokens, place among the segment's chunks (consecutive per segment); seg_chunks [n_segs, 2] =
 // first chunk, chunks.  carry [n_chunks, H, dim, vdim] and decay_prod [n_chunks, H, dim] are scratch for segments
 // of several chunks.  out [T, H, vdim] float32.  z [T, H * dim] float32 holds the decay logits and is overwritten
-// (with the decays) when a segment has several chunks.
+// (with the decays) when a segment has several chunks.  k_fac [T, H] (or null) multiplies a token's keys per head,
+// in 32 bits; a_head [T, H] (or null) gives one decay per (token, head) in place of z; with ones_col = 1 the last of
+// the vdim value columns is 1 for every token and v holds vdim - 1 columns per head.
 int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
                  long long v_stride, int dtype, float* z, const float* z_bias, float tau, float q_scale,
                  float* state, int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs,
                  const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, int any_single, int any_multi,
                  float* carry, float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
-                 void* stream);
+                 const float* k_fac, const float* a_head, int ones_col, void* stream);
 // Short causal convolution over time with a residual (shortconv.cu): out[t, c] = x[t, c] + sum_j w[c, j] *
 // in(t - taps + 1 + j, c) over the request's own inputs; the last taps - 1 inputs of every request live in its
 // state slot (state [n_slots, taps - 1, channels] float32, oldest first; zeros before the sequence's start) and are
@@ -157,15 +159,11 @@ int ftk_latent_query_rotate(const void* q, int dtype, int n_heads, int flat_dim,
                             const int32_t* positions, const float* table, int max_pos, void* q_out, int kv_rank,
                             int pad_dim, int n_tokens, void* stream);
 // Matrix memory with exponential gates (mlstm.cu): see the file's header.  pre [T, 2 * heads] float32 = input gate
-// then forget gate before bias and cap; m_state [n_slots, heads]; gate_i, logit_f, m_out [T, heads].
+// then forget gate before bias and cap; m_state [n_slots, heads]; key_fac = e^(input gate), decay = e^(forget gate)
+// and m_out, all [T, heads].
 int ftk_mlstm_gates(const float* pre, const float* bias_i, const float* bias_f, float cap, float* m_state, int n_slots,
                     const int32_t* state_slots, const int32_t* seg_info, int n_segs, int n_heads, int n_tokens,
-                    float* gate_i, float* logit_f, float* m_out, void* stream);
-// proj rows hold [q heads*dim | k heads*dim | v heads*vdim | ...]; q32, k32 [T, heads*dim], v32 [T, heads*(vdim+1)],
-// z [T, heads*dim] float32.
-int ftk_mlstm_prepare(const void* proj, int dtype, long long row_stride, int n_heads, int dim, int vdim,
-                      const float* gate_i, const float* logit_f, float* q32, float* k32, float* v32, float* z,
-                      int n_tokens, void* stream);
+                    float* key_fac, float* decay, float* m_out, void* stream);
 // o32 [T, heads, vdim + 1] (the last column is n . q); out [T, heads * vdim] of `dtype`.
 int ftk_mlstm_output(const float* o32, const float* m, const void* gates, long long gate_stride, const float* norm_w,
                      float eps, void* out, int dtype, int n_tokens, int n_heads, int vdim, void* stream);

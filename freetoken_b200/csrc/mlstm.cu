@@ -7,10 +7,11 @@
 // (one decay per head) and o_t = C_t^T q_t / (max(|N_t . q_t|, 1) + 1e-6 e^(m_t)); N is the recurrence of one more
 // value column that is 1 for every token.  The gates are capped (|i_t| <= cap, f_t = logsigmoid of a capped
 // value), so C stays far inside the 32-bit range, and floating-point numbers keep their relative precision
-// under the change of scale.  Three kernels around the recurrence kernel:
-//   gates    per (request, head), a warp: the capped gates and m_t of the step's tokens (two warp scans per 32 tokens:
+// under the change of scale.  Two kernels around the recurrence kernel, which reads q, k and v where the projection
+// left them, multiplies the keys by e^(i_t) in 32 bits as it stages them, takes e^(f_t) as the head's decay and adds
+// the column of ones itself:
+//   gates    per (request, head), a warp: e^(i_t), e^(f_t) and m_t of the step's tokens (two warp scans per 32 tokens:
 //            F_t = f_1 + ... + f_t, m_t = F_t + max(m_0, max_(s <= t) (i_s - F_s))), m left in the request's slot;
-//   prepare  per token: q, e^(i_t) k and [v | 1] in 32-bit, the forget gate's logit once per key channel;
 //   output   per (token, head): the division, the head's unit norm, the weight, the sigmoid gate.
 #include "common.cuh"
 
@@ -22,7 +23,7 @@ __device__ __forceinline__ float log_sigmoid(float z) { return z > 0.f ? -log1pf
 __global__ void mlstm_gates_kernel(const float* __restrict__ pre, const float* __restrict__ bias_i,
                                    const float* __restrict__ bias_f, float cap, float* __restrict__ m_state, int n_slots,
                                    const int32_t* __restrict__ state_slots, const int32_t* __restrict__ seg_info, int n_segs,
-                                   int H, int n_tokens, float* __restrict__ gate_i, float* __restrict__ logit_f,
+                                   int H, int n_tokens, float* __restrict__ key_fac, float* __restrict__ decay,
                                    float* __restrict__ m_out) {
   pdl_wait();
   pdl_trigger();
@@ -37,12 +38,11 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, const float* _
   for (int t0 = 0; t0 < q_len; t0 += 32) {
     const int t = t0 + lane;
     const bool on = t < q_len;
-    float gi = -INFINITY, f = 0.f, zf = 0.f;
+    float gi = -INFINITY, f = 0.f;
     if (on) {
       const float* row = pre + (size_t)(q_start + t) * 2 * H;
       gi = capped(row[h] + bias_i[h], cap);
-      zf = capped(row[H + h] + bias_f[h], cap);
-      f = log_sigmoid(zf);
+      f = log_sigmoid(capped(row[H + h] + bias_f[h], cap));
     }
     float F = f;  // inclusive sum of the forget gates over the lanes
 #pragma unroll
@@ -59,36 +59,14 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, const float* _
     const float mt = F + fmaxf(m, best);
     if (on) {
       const size_t at = (size_t)(q_start + t) * H + h;
-      gate_i[at] = gi;
-      logit_f[at] = zf;
+      key_fac[at] = expf(gi);
+      decay[at] = expf(f);
       m_out[at] = mt;
     }
     const int last = min(31, q_len - t0 - 1);
     m = __shfl_sync(0xffffffffu, mt, last);
   }
   if (has_slot && lane == 0) m_state[(size_t)slot * H + h] = m;
-}
-
-template <typename T>
-__global__ void mlstm_prepare_kernel(const T* __restrict__ proj, long long row_stride, int H, int D, int Dv,
-                                     const float* __restrict__ gate_i, const float* __restrict__ logit_f,
-                                     float* __restrict__ q32, float* __restrict__ k32, float* __restrict__ v32,
-                                     float* __restrict__ z) {
-  pdl_wait();
-  pdl_trigger();
-  const int t = blockIdx.x;
-  const T* row = proj + (size_t)t * row_stride;
-  const int HD = H * D, HV = H * (Dv + 1);
-  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
-    const int h = i / D;
-    q32[(size_t)t * HD + i] = to_float(row[i]);
-    k32[(size_t)t * HD + i] = expf(gate_i[(size_t)t * H + h]) * to_float(row[HD + i]);
-    z[(size_t)t * HD + i] = logit_f[(size_t)t * H + h];
-  }
-  for (int i = threadIdx.x; i < HV; i += blockDim.x) {
-    const int h = i / (Dv + 1), d = i - h * (Dv + 1);
-    v32[(size_t)t * HV + i] = d < Dv ? to_float(row[2 * HD + h * Dv + d]) : 1.f;
-  }
 }
 
 // a warp per (token, head)
@@ -125,33 +103,15 @@ using namespace ftk;
 
 extern "C" int ftk_mlstm_gates(const float* pre, const float* bias_i, const float* bias_f, float cap, float* m_state,
                                int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs, int n_heads,
-                               int n_tokens, float* gate_i, float* logit_f, float* m_out, void* stream) {
+                               int n_tokens, float* key_fac, float* decay, float* m_out, void* stream) {
   FTK_REQUIRE(n_segs >= 1 && n_heads >= 1 && n_tokens >= 0 && cap > 0.f, "mlstm_gates: bad sizes");
   if (n_tokens == 0) return 0;
-  FTK_REQUIRE(pre && bias_i && bias_f && m_state && state_slots && seg_info && gate_i && logit_f && m_out,
+  FTK_REQUIRE(pre && bias_i && bias_f && m_state && state_slots && seg_info && key_fac && decay && m_out,
               "mlstm_gates: null pointer");
   const int warps = n_segs * n_heads;
   FTK_LAUNCH(mlstm_gates_kernel, (warps + 3) / 4, 128, 0, (cudaStream_t)stream, pre, bias_i, bias_f, cap, m_state, n_slots,
-             state_slots, seg_info, n_segs, n_heads, n_tokens, gate_i, logit_f, m_out);
+             state_slots, seg_info, n_segs, n_heads, n_tokens, key_fac, decay, m_out);
   FTK_LAUNCH_CHECK("mlstm_gates");
-  return 0;
-}
-
-extern "C" int ftk_mlstm_prepare(const void* proj, int dtype, long long row_stride, int n_heads, int dim, int vdim,
-                                 const float* gate_i, const float* logit_f, float* q32, float* k32, float* v32, float* z,
-                                 int n_tokens, void* stream) {
-  FTK_REQUIRE(dtype_ok(dtype) && n_heads >= 1 && dim >= 1 && vdim >= 1 && n_tokens >= 0, "mlstm_prepare: bad arguments");
-  if (n_tokens == 0) return 0;
-  FTK_REQUIRE(proj && gate_i && logit_f && q32 && k32 && v32 && z, "mlstm_prepare: null pointer");
-  cudaStream_t s = (cudaStream_t)stream;
-  const int threads = n_heads * dim >= 1024 ? 256 : 128;
-  if (dtype == FTK_F32)
-    FTK_LAUNCH(mlstm_prepare_kernel<float>, n_tokens, threads, 0, s, (const float*)proj, row_stride, n_heads, dim, vdim, gate_i,
-               logit_f, q32, k32, v32, z);
-  else
-    FTK_LAUNCH(mlstm_prepare_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)proj, row_stride, n_heads, dim,
-               vdim, gate_i, logit_f, q32, k32, v32, z);
-  FTK_LAUNCH_CHECK("mlstm_prepare");
   return 0;
 }
 

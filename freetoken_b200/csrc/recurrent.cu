@@ -51,12 +51,18 @@ struct GlaArgs {
   float* decay_prod;       // [n_chunks, H, D]
   float* out;              // [T, H, Dv]
   int H, D, Dv, n_tokens, groups;
+  const float* k_fac;      // [T, H] or null: a factor on token t's keys of head h (applied in 32 bits while they are staged)
+  const float* a_head;     // [T, H] or null: one decay per (token, head) for all key channels, in place of z
+  int ones_col;            // 1: the last of the Dv value columns is 1 for every token, and v holds Dv - 1 columns per head
 };
 
 // 16 bytes from global to shared memory without a trip through registers; `valid` false writes zeros
 __device__ __forceinline__ void gla_cp16(void* dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void gla_cp4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
 }
 __device__ __forceinline__ void gla_cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void gla_cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
@@ -84,6 +90,7 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
   pdl_trigger();
   extern __shared__ __align__(16) float sm[];
   const int D = a.D, Dv = a.Dv;
+  const int Dvin = Dv - a.ones_col;             // value columns that v holds
   const int Dp = DPT * kGlaSlices;              // padded key channels
   constexpr int NC = gla_cols_per_thread(DPT);
   constexpr int kGlaCols = 32 * NC;             // value columns per group of four warps
@@ -141,11 +148,12 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
   // values as they lie in memory into a second set of buffers while the current 16 are worked on, and a pass
   // from shared to shared memory widens them
   // (a chunk of one batch has nothing to fetch ahead of: it takes the direct way)
-  const bool ahead = wide && ntok > kGlaBatch && Dv % 8 == 0 && a.v_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15) == 0;
+  const bool ahead = wide && ntok > kGlaBatch && Dvin % 8 == 0 && a.v_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15) == 0;
   __nv_bfloat16* kraw = reinterpret_cast<__nv_bfloat16*>(part + kGlaSlices * kGlaBatch * cols);  // [batch][Dp]
   __nv_bfloat16* qraw = kraw + kGlaBatch * Dp;
   float* zraw = reinterpret_cast<float*>(qraw + kGlaBatch * Dp);                                  // [batch][Dp]
   __nv_bfloat16* vraw = reinterpret_cast<__nv_bfloat16*>(zraw + kGlaBatch * Dp);                  // [batch][cols]
+  float* hraw = reinterpret_cast<float*>(vraw + kGlaBatch * cols);                                // [2][batch]: key factors, head decays
   auto fetch = [&](int b0n) {
     const int nbn = min(kGlaBatch, ntok - b0n);
     const int per_row = Dp / 8;
@@ -158,16 +166,25 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
       const bool in = d < D;
       gla_cp16(kraw + t * Dp + d, in ? kg + tok * a.k_stride + (size_t)h * D + d : kg, in);
       if (MODE != 1) gla_cp16(qraw + t * Dp + d, in ? qg + tok * a.q_stride + (size_t)h * D + d : qg, in);
-      const float* zr = in ? a.z + (tok * a.H + h) * D + d : a.z;
-      gla_cp16(zraw + t * Dp + d, zr, in);
-      gla_cp16(zraw + t * Dp + d + 4, in ? zr + 4 : zr, in);
+      if (!a.a_head) {
+        const float* zr = in ? a.z + (tok * a.H + h) * D + d : a.z;
+        gla_cp16(zraw + t * Dp + d, zr, in);
+        gla_cp16(zraw + t * Dp + d + 4, in ? zr + 4 : zr, in);
+      }
+    }
+    if (a.k_fac || a.a_head) {
+      for (int t = threadIdx.x; t < nbn; t += blockDim.x) {
+        const size_t at = (size_t)(q_start + tok0 + b0n + t) * a.H + h;
+        if (a.k_fac) gla_cp4(hraw + t, a.k_fac + at);
+        if (a.a_head) gla_cp4(hraw + kGlaBatch + t, a.a_head + at);
+      }
     }
     const int vper = cols / 8;
     for (int i = threadIdx.x; i < nbn * vper; i += blockDim.x) {
       const int t = i / vper, j = (i % vper) * 8;
       const size_t tok = (size_t)(q_start + tok0 + b0n + t);
-      const bool in = col0 + j < Dv;
-      gla_cp16(vraw + t * cols + j, in ? vg + tok * a.v_stride + (size_t)h * Dv + col0 + j : vg, in);
+      const bool in = col0 + j < Dvin;
+      gla_cp16(vraw + t * cols + j, in ? vg + tok * a.v_stride + (size_t)h * Dvin + col0 + j : vg, in);
     }
     gla_cp_commit();
   };
@@ -178,19 +195,26 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
     __syncthreads();
     if (sizeof(T) == 2 && ahead) {
       for (int i = threadIdx.x * 4; i < nb * Dp; i += blockDim.x * 4) {
-        const int d = i % Dp;
+        const int d = i % Dp, t = i / Dp;
+        const float kf = a.k_fac ? hraw[t] : 1.f;
         const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(kraw + i);
         const float2 k01 = __bfloat1622float2(k2[0]), k23 = __bfloat1622float2(k2[1]);
-        *reinterpret_cast<float4*>(sk + i) = make_float4(k01.x, k01.y, k23.x, k23.y);
+        *reinterpret_cast<float4*>(sk + i) = make_float4(k01.x * kf, k01.y * kf, k23.x * kf, k23.y * kf);
         if (MODE != 1) {
           const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(qraw + i);
           const float2 q01 = __bfloat1622float2(q2[0]), q23 = __bfloat1622float2(q2[1]);
           *reinterpret_cast<float4*>(sq + i) = make_float4(q01.x * a.q_scale, q01.y * a.q_scale, q23.x * a.q_scale, q23.y * a.q_scale);
         }
-        float4 av = *reinterpret_cast<const float4*>(zraw + i);
+        float4 av;
         if (d >= D) {
           av = make_float4(1.f, 1.f, 1.f, 1.f);
-        } else if (!a.z_is_decay) {
+        } else if (a.a_head) {
+          const float ah = hraw[kGlaBatch + t];
+          av = make_float4(ah, ah, ah, ah);
+        } else {
+          av = *reinterpret_cast<const float4*>(zraw + i);
+        }
+        if (d < D && !a.a_head && !a.z_is_decay) {
           const float* bz = a.z_bias ? a.z_bias + (size_t)h * D + d : nullptr;
           av.x = decay_of(av.x + (bz ? bz[0] : 0.f), a.inv_tau);
           av.y = decay_of(av.y + (bz ? bz[1] : 0.f), a.inv_tau);
@@ -203,6 +227,7 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
         const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vraw + i));
         sv[i] = f.x;
         sv[i + 1] = f.y;
+        if (a.ones_col && col0 + i % cols == Dvin) sv[i] = 1.f;  // Dvin is a multiple of 8 here, i is even
       }
       __syncthreads();
       if (b0 + kGlaBatch < ntok) fetch(b0 + kGlaBatch);  // the buffers are read: the next batch may land
@@ -219,17 +244,25 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
           const uint4 kr = *reinterpret_cast<const uint4*>(kb + tok * a.k_stride + (size_t)h * D + d);
           const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kr);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(k2[u]); kv[2 * u] = f.x; kv[2 * u + 1] = f.y; }
+          const float kf = a.k_fac ? a.k_fac[tok * a.H + h] : 1.f;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(k2[u]); kv[2 * u] = f.x * kf; kv[2 * u + 1] = f.y * kf; }
           if (MODE != 1) {
             const uint4 qr = *reinterpret_cast<const uint4*>(qb + tok * a.q_stride + (size_t)h * D + d);
             const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qr);
 #pragma unroll
             for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(q2[u]); qv[2 * u] = f.x * a.q_scale; qv[2 * u + 1] = f.y * a.q_scale; }
           }
-          const float* zr = a.z + (tok * a.H + h) * D + d;
-          const float4 z0 = *reinterpret_cast<const float4*>(zr), z1 = *reinterpret_cast<const float4*>(zr + 4);
-          av[0] = z0.x; av[1] = z0.y; av[2] = z0.z; av[3] = z0.w; av[4] = z1.x; av[5] = z1.y; av[6] = z1.z; av[7] = z1.w;
-          if (!a.z_is_decay) {
+          if (a.a_head) {
+            const float ah = a.a_head[tok * a.H + h];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) av[u] = ah;
+          } else {
+            const float* zr = a.z + (tok * a.H + h) * D + d;
+            const float4 z0 = *reinterpret_cast<const float4*>(zr), z1 = *reinterpret_cast<const float4*>(zr + 4);
+            av[0] = z0.x; av[1] = z0.y; av[2] = z0.z; av[3] = z0.w; av[4] = z1.x; av[5] = z1.y; av[6] = z1.z; av[7] = z1.w;
+          }
+          if (!a.a_head && !a.z_is_decay) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) av[u] = decay_of(av[u] + (a.z_bias ? a.z_bias[(size_t)h * D + d + u] : 0.f), a.inv_tau);
           }
@@ -249,9 +282,9 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
         float qv = 0.f, kv = 0.f, av = 1.f;
         if (d < D) {
           if (MODE != 1) qv = to_float(qb[tok * a.q_stride + (size_t)h * D + d]) * a.q_scale;
-          kv = to_float(kb[tok * a.k_stride + (size_t)h * D + d]);
-          av = a.z[(tok * a.H + h) * D + d];
-          if (!a.z_is_decay) av = decay_of(av + (a.z_bias ? a.z_bias[(size_t)h * D + d] : 0.f), a.inv_tau);
+          kv = to_float(kb[tok * a.k_stride + (size_t)h * D + d]) * (a.k_fac ? a.k_fac[tok * a.H + h] : 1.f);
+          av = a.a_head ? a.a_head[tok * a.H + h] : a.z[(tok * a.H + h) * D + d];
+          if (!a.a_head && !a.z_is_decay) av = decay_of(av + (a.z_bias ? a.z_bias[(size_t)h * D + d] : 0.f), a.inv_tau);
         }
         sq[i] = qv; sk[i] = kv; sa[i] = av;
       }
@@ -259,7 +292,8 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
     for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
       const int t = i / cols, j = i % cols;
       const size_t tok = (size_t)(q_start + tok0 + b0 + t);
-      sv[i] = col0 + j < Dv ? to_float(vb[tok * a.v_stride + (size_t)h * Dv + col0 + j]) : 0.f;
+      sv[i] = col0 + j < Dvin ? to_float(vb[tok * a.v_stride + (size_t)h * Dvin + col0 + j])
+                              : (a.ones_col && col0 + j == Dvin ? 1.f : 0.f);
     }
     __syncthreads();
     }
@@ -366,7 +400,7 @@ static int launch_gla(GlaArgs a, bool any_single, bool any_multi, cudaStream_t s
   size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols) *
                 sizeof(float);
   if (sizeof(T) == 2)  // the next batch as it lies in memory: q, k (bfloat16), decay logits (float), values (bfloat16)
-    smem += (size_t)kGlaBatch * Dp * (2 + 2 + 4) + (size_t)kGlaBatch * cols * 2;
+    smem += (size_t)kGlaBatch * Dp * (2 + 2 + 4) + (size_t)kGlaBatch * cols * 2 + (size_t)2 * kGlaBatch * 4;
   dim3 grid(a.n_chunks, a.H, (a.Dv + cols - 1) / cols);
   auto k0 = gla_chunk_kernel<T, DPT, 0>;
   auto k1 = gla_chunk_kernel<T, DPT, 1>;
@@ -376,7 +410,7 @@ static int launch_gla(GlaArgs a, bool any_single, bool any_multi, cudaStream_t s
     cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
-  if (any_multi) {  // the decays of all of the step's tokens, once, where the logits lay
+  if (any_multi && !a.a_head) {  // the decays of all of the step's tokens, once, where the logits lay
     const long long n = (long long)a.n_tokens * a.H * a.D;
     const unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     FTK_LAUNCH(gla_decay_kernel, blocks, 256, 0, s, a.z, a.z_bias, n, a.H * a.D, a.inv_tau);
@@ -410,7 +444,7 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
                             const int32_t* seg_info, int n_segs, const int32_t* chunks, int n_chunks,
                             const int32_t* seg_chunks, int any_single, int any_multi, float* carry,
                             float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
-                            void* stream) {
+                            const float* k_fac, const float* a_head, int ones_col, void* stream) {
   FTK_REQUIRE(dtype_ok(dtype), "gla_scan: bad dtype %d", dtype);
   FTK_REQUIRE(n_tokens >= 0 && n_segs >= 0 && n_chunks >= 0, "gla_scan: bad counts");
   if (n_tokens == 0 || n_chunks == 0) return 0;
@@ -419,7 +453,8 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
               dim, vdim);
   FTK_REQUIRE(n_segs <= 65535, "gla_scan: too many segments");
   FTK_REQUIRE(tau > 0.f, "gla_scan: tau must be positive");
-  FTK_REQUIRE(q && k && v && z && state && state_slots && seg_info && chunks && seg_chunks && out,
+  FTK_REQUIRE(ones_col == 0 || (ones_col == 1 && vdim >= 2), "gla_scan: a column of ones needs a value column beside it");
+  FTK_REQUIRE(q && k && v && (z || a_head) && state && state_slots && seg_info && chunks && seg_chunks && out,
               "gla_scan: null pointer");
   FTK_REQUIRE(!any_multi || (carry && decay_prod), "gla_scan: portions of several chunks need scratch");
   GlaArgs a;
@@ -427,6 +462,7 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
   a.z = z; a.z_bias = z_bias; a.z_is_decay = 0; a.groups = 1; a.inv_tau = 1.f / tau; a.q_scale = q_scale;
   a.state = state; a.state_slots = state_slots; a.seg_info = seg_info; a.chunks = chunks; a.seg_chunks = seg_chunks;
   a.n_chunks = n_chunks; a.n_segs = n_segs; a.n_slots = n_slots; a.carry = carry; a.decay_prod = decay_prod;
+  a.k_fac = k_fac; a.a_head = a_head; a.ones_col = ones_col;
   a.out = out; a.H = n_heads; a.D = dim; a.Dv = vdim; a.n_tokens = n_tokens;
   cudaStream_t s = (cudaStream_t)stream;
   note_variant(any_multi ? "gla_scan: chunks side by side" : "gla_scan: one chunk per request");

@@ -362,10 +362,6 @@ def bench_kekopel(a) -> dict:
     add("mlstm_gates", lambda: ops.mlstm_gates(pre, bias[:H], bias[H:], 15.0, m_state, slots, seg, len(segs), gi, zf, m),
         T * H * 4 * 5)
     wide = (torch.randn(T, H * (2 * D + 2 * Dv), device=dev, generator=g) * 0.3).to(bf)
-    q32, k32, z = (torch.empty(T, H * D, device=dev) for _ in range(3))
-    v32 = torch.empty(T, H * (Dv + 1), device=dev)
-    add("mlstm_prepare", lambda: ops.mlstm_prepare(wide, H, D, Dv, gi, zf, q32, k32, v32, z),
-        T * H * ((2 * D + Dv) * 2 + (3 * D + Dv + 1) * 4))
     chunks, per_seg, single, multi = chunk_list(segs, a.chunk)
     n = chunks.shape[0]
     state = torch.zeros(n_slots, H, D, Dv + 1, device=dev)
@@ -374,10 +370,11 @@ def bench_kekopel(a) -> dict:
     o32 = torch.empty(T, H, Dv + 1, device=dev)
     cd, pd = torch.from_numpy(chunks).to(dev), torch.from_numpy(per_seg).to(dev)
     passes = 2 if multi else 1
-    add("gla_scan (32-bit inputs, the normaliser as one more value column)",
-        lambda: ops.gla_scan(q32, k32, v32, z, None, 1.0, D ** -0.5, state, slots, seg, len(segs), cd, n, pd, single, multi,
-                             carry, decay, o32),
-        T * H * (3 * D + Dv + 1) * 4 * passes + T * H * (Dv + 1) * 4 + (2 * len(segs) + (2 * n if multi else 0)) * H * D * (Dv + 1) * 4,
+    add("gla_scan (a key factor and a decay per head, the normaliser as a column of ones)",
+        lambda: ops.gla_scan(wide[:, :H * D], wide[:, H * D:2 * H * D], wide[:, 2 * H * D:H * (2 * D + Dv)], None, None, 1.0,
+                             D ** -0.5, state, slots, seg, len(segs), cd, n, pd, single, multi, carry, decay, o32,
+                             k_fac=gi, a_head=zf, ones_col=True),
+        T * H * ((2 * D + Dv) * 2 + 8) * passes + T * H * (Dv + 1) * 4 + (2 * len(segs) + (2 * n if multi else 0)) * H * D * (Dv + 1) * 4,
         T * H * D * (Dv + 1) * (8 if multi else 5))
     o = torch.empty(T, H * Dv, dtype=bf, device=dev)
     nw = torch.ones(H * Dv, device=dev)

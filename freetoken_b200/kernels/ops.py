@@ -143,10 +143,9 @@ _SIGNATURES = {
                          ctypes.c_longlong, _vp, _i, _i, _vp],
     "ftk_latent_query_rotate": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "ftk_mlstm_gates": [_vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
-    "ftk_mlstm_prepare": [_vp, _i, ctypes.c_longlong, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
     "ftk_mlstm_output": [_vp, _vp, _vp, ctypes.c_longlong, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "ftk_gla_scan": [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _i, _vp, _vp, _f, _f,
-                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp],
 }
 _bound = False
 _launches = 0
@@ -1072,7 +1071,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
              tau: float, q_scale: float, state: torch.Tensor, state_slots: torch.Tensor, seg_info: torch.Tensor,
              n_segs: int, chunks: torch.Tensor, n_chunks: int, seg_chunks: torch.Tensor, any_single: bool,
              any_multi: bool, carry: Optional[torch.Tensor], decay_prod: Optional[torch.Tensor],
-             out: torch.Tensor) -> None:
+             out: torch.Tensor, k_fac: Optional[torch.Tensor] = None, a_head: Optional[torch.Tensor] = None,
+             ones_col: bool = False) -> None:
     """Gated linear attention of the step's tokens, per (request, head):
     ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t q_scale)``, ``a_t = sigmoid(z_t + z_bias)^(1 / tau)``.
 
@@ -1081,12 +1081,20 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     the slot ``state_slots[segment]`` (a segment with ``kv_len == q_len`` starts from zero);
     ``chunks [n, 4]`` / ``seg_chunks [S, 2]`` from :func:`freetoken_b200.parts.gla.chunk_list`; ``carry
     [n, H, D, Dv]`` and ``decay_prod [n, H, D]`` float32 scratch for segments of several chunks;
-    ``out [T, H, Dv]`` float32."""
+    ``out [T, H, Dv]`` float32.
+
+    ``k_fac [T, H]`` float32 multiplies a token's keys of a head (in 32 bits, as they are read); ``a_head [T, H]``
+    float32 gives one decay per (token, head) for all key channels, and ``z`` is then ``None``; with ``ones_col``
+    the state's last value column belongs to a value that is 1 for every token, and ``v`` is ``[T, H * (Dv - 1)]``
+    (the sum of the keys under the same decays: a normaliser)."""
     T = out.shape[0]
     H, D, Dv = state.shape[1], state.shape[2], state.shape[3]
-    if q.shape != (T, H * D) or k.shape != (T, H * D) or v.shape != (T, H * Dv) or out.shape != (T, H, Dv) \
-            or z.shape != (T, H * D):
+    if q.shape != (T, H * D) or k.shape != (T, H * D) or v.shape != (T, H * (Dv - (1 if ones_col else 0))) \
+            or out.shape != (T, H, Dv) or (z is None) == (a_head is None) or (z is not None and z.shape != (T, H * D)):
         raise KernelError("gla_scan: shapes do not agree")
+    for name, f in (("k_fac", k_fac), ("a_head", a_head)):
+        if f is not None and (f.shape != (T, H) or not f.is_contiguous()):
+            raise KernelError(f"gla_scan: {name} must be a contiguous [T, H]")
     if q.dtype != k.dtype or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
         raise KernelError("gla_scan: q, k, v must share a dtype and have adjacent columns")
     if z_bias is not None and z_bias.numel() != H * D:
@@ -1096,7 +1104,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         raise KernelError("gla_scan: scratch for segments of several chunks is missing or too small")
     if chunks.numel() < 4 * n_chunks or seg_chunks.numel() < 2 * n_segs:
         raise KernelError("gla_scan: chunk lists too short")
-    launches = (1 if any_single else 0) + (4 if any_multi else 0)
+    launches = (1 if any_single else 0) + ((4 if a_head is None else 3) if any_multi else 0)
     _check(_lib().ftk_gla_scan(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _code(q, "q"),
         _dev(z, "z", torch.float32), _dev(z_bias, "z_bias", torch.float32), float(tau), float(q_scale),
@@ -1104,7 +1112,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         _dev(seg_info, "seg_info", torch.int32), n_segs, _dev(chunks, "chunks", torch.int32), n_chunks,
         _dev(seg_chunks, "seg_chunks", torch.int32), 1 if any_single else 0, 1 if any_multi else 0,
         _dev(carry, "carry", torch.float32), _dev(decay_prod, "decay_prod", torch.float32),
-        _dev(out, "out", torch.float32), T, H, D, Dv, _stream()), "gla_scan", max(1, launches))
+        _dev(out, "out", torch.float32), T, H, D, Dv, _dev(k_fac, "k_fac", torch.float32),
+        _dev(a_head, "a_head", torch.float32), 1 if ones_col else 0, _stream()), "gla_scan", max(1, launches))
 
 
 # --------------------------------------------------------------------------- short convolution, depth mix
@@ -1215,39 +1224,22 @@ def heads_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 # --------------------------------------------------------------------------- matrix memory with exponential gates
 def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, m_state: torch.Tensor,
-                state_slots: torch.Tensor, seg_info: torch.Tensor, n_segs: int, gate_i: torch.Tensor,
-                logit_f: torch.Tensor, m_out: torch.Tensor) -> None:
-    """Gates of a matrix-memory layer for the step's tokens, per (request, head), all float32:
-    ``gate_i = cap tanh((pre_i + b_i) / cap)``, ``logit_f = cap tanh((pre_f + b_f) / cap)`` (the forget gate is
-    ``logsigmoid(logit_f)``), and the running maximum ``m_t = max(f_t + m_(t-1), i_t)``, which starts from
+                state_slots: torch.Tensor, seg_info: torch.Tensor, n_segs: int, key_fac: torch.Tensor,
+                decay: torch.Tensor, m_out: torch.Tensor) -> None:
+    """Gates of a matrix-memory layer for the step's tokens, per (request, head), all float32: with
+    ``i = cap tanh((pre_i + b_i) / cap)`` and ``f = logsigmoid(cap tanh((pre_f + b_f) / cap))``, ``key_fac = e^i``,
+    ``decay = e^f``, and the running maximum ``m_t = max(f_t + m_(t-1), i_t)``, which starts from
     ``m_state[slot, head]`` (from 0 for a request's first tokens) and is left there.  ``pre [T, 2 H]``."""
     T, H2 = pre.shape
     H = H2 // 2
-    if gate_i.shape != (T, H) or logit_f.shape != (T, H) or m_out.shape != (T, H) or m_state.shape[1:] != (H,):
+    if key_fac.shape != (T, H) or decay.shape != (T, H) or m_out.shape != (T, H) or m_state.shape[1:] != (H,):
         raise KernelError("mlstm_gates: shapes do not agree")
     _check(_lib().ftk_mlstm_gates(
         _dev(pre, "pre", torch.float32), _dev(bias_i, "bias_i", torch.float32), _dev(bias_f, "bias_f", torch.float32),
         float(cap), _dev(m_state, "m_state", torch.float32), m_state.shape[0],
         _dev(state_slots, "state_slots", torch.int32), _dev(seg_info, "seg_info", torch.int32), n_segs, H, T,
-        _dev(gate_i, "gate_i", torch.float32), _dev(logit_f, "logit_f", torch.float32),
+        _dev(key_fac, "key_fac", torch.float32), _dev(decay, "decay", torch.float32),
         _dev(m_out, "m_out", torch.float32), _stream()), "mlstm_gates")
-
-
-def mlstm_prepare(proj: torch.Tensor, n_heads: int, dim: int, vdim: int, gate_i: torch.Tensor, logit_f: torch.Tensor,
-                  q32: torch.Tensor, k32: torch.Tensor, v32: torch.Tensor, z: torch.Tensor) -> None:
-    """Inputs of the linear recurrence that a matrix-memory layer runs on, all float32: ``q32 = q``,
-    ``k32 = e^(gate_i) k``, ``v32 = [v | 1]`` per head (the extra column carries the normaliser), ``z`` the forget
-    gate's logit once per key channel.  ``proj [T, >= H (2 dim + vdim)]`` holds q, k, v side by side."""
-    T = proj.shape[0]
-    H = n_heads
-    if proj.shape[1] < H * (2 * dim + vdim) or proj.stride(1) != 1 or q32.shape != (T, H * dim) \
-            or k32.shape != (T, H * dim) or v32.shape != (T, H * (vdim + 1)) or z.shape != (T, H * dim):
-        raise KernelError("mlstm_prepare: shapes do not agree")
-    _check(_lib().ftk_mlstm_prepare(
-        _dev(proj, "proj"), _code(proj, "proj"), proj.stride(0) if T > 1 else proj.shape[1], H, dim, vdim,
-        _dev(gate_i, "gate_i", torch.float32), _dev(logit_f, "logit_f", torch.float32), _dev(q32, "q32", torch.float32),
-        _dev(k32, "k32", torch.float32), _dev(v32, "v32", torch.float32), _dev(z, "z", torch.float32), T, _stream()),
-        "mlstm_prepare")
 
 
 def mlstm_output(o32: torch.Tensor, m: torch.Tensor, gates: torch.Tensor, norm_weight: torch.Tensor, eps: float,

@@ -12,8 +12,9 @@ by ``sigmoid(W_g h_t)``, and projected.
 
 The state is kept as ``C_t = e^(m_t) S_t`` and ``N_t = e^(m_t) n_t`` (one tensor ``[H, D, Dv + 1]``: ``N`` is the
 recurrence of one more value column that is 1 for every token) and ``m_t``; then ``C_t = e^(f_t) C_(t-1) +
-(e^(i_t) k_t) v_t^T`` is the linear recurrence that :func:`ops.gla_scan` runs (with one decay per head), chunked
-over long portions, and ``o_t = C_t^T q_t / (max(|N_t . q_t|, 1) + 1e-6 e^(m_t))``.  The capped gates keep ``C``
+(e^(i_t) k_t) v_t^T`` is the linear recurrence that :func:`ops.gla_scan` runs, chunked over long portions: it reads
+``q, k, v`` where the projection left them, multiplies a token's keys by ``e^(i_t)`` in 32 bits as it stages them,
+takes ``e^(f_t)`` as the head's one decay and adds the column of ones itself; and ``o_t = C_t^T q_t / (max(|N_t . q_t|, 1) + 1e-6 e^(m_t))``.  The capped gates keep ``C``
 far inside the 32-bit range.  Gates, state, the inputs of the recurrence and the output's norm are 32-bit;
 the projections are library products.  The state lives in a slot of the cache manager's state pool and starts
 from zero (and ``m`` from 0) for a request's first tokens.  The reference has no recurrent mixer.
@@ -80,7 +81,7 @@ class MatrixMemory(Mixer):
     def workspace_bytes(self, n_tokens: int) -> int:
         item = 4 if self.env.dtype == torch.float32 else 2
         H, D, Dv = self.n_heads, self.head_dim, self.v_dim
-        rows = n_tokens * ((self.proj_rows + H * Dv + self.hidden) * item + (3 * H * D + 2 * H * (Dv + 1) + 5 * H) * 4)
+        rows = n_tokens * ((self.proj_rows + H * Dv + self.hidden) * item + (H * (Dv + 1) + 5 * H) * 4)
         return rows + self.max_chunks(n_tokens) * H * D * (Dv + 2) * 4
 
     def prepare(self, builder) -> None:
@@ -107,17 +108,12 @@ class MatrixMemory(Mixer):
         ops.linear(h, self.params["in_proj.weight"], proj)
         pre = ws.get("mlstm.pre", (T, 2 * H), f32, (cap, 2 * H))
         ops.linear_f32(h, self.params["gate_proj.weight"], pre)
-        gi = ws.get("mlstm.gate_i", (T, H), f32, (cap, H))
-        zf = ws.get("mlstm.logit_f", (T, H), f32, (cap, H))
+        kf = ws.get("mlstm.key_fac", (T, H), f32, (cap, H))
+        dec = ws.get("mlstm.decay_t", (T, H), f32, (cap, H))
         m = ws.get("mlstm.m", (T, H), f32, (cap, H))
         bias = self.params["gate_proj.bias"]
         ops.mlstm_gates(pre, bias[:H], bias[H:], self.cap, cache.tensors["m"], step.state_slots, step.seg_info,
-                        len(step.segments), gi, zf, m)
-        q32 = ws.get("mlstm.q32", (T, H * D), f32, (cap, H * D))
-        k32 = ws.get("mlstm.k32", (T, H * D), f32, (cap, H * D))
-        v32 = ws.get("mlstm.v32", (T, H * (Dv + 1)), f32, (cap, H * (Dv + 1)))
-        z = ws.get("mlstm.z", (T, H * D), f32, (cap, H * D))
-        ops.mlstm_prepare(proj, H, D, Dv, gi, zf, q32, k32, v32, z)
+                        len(step.segments), kf, dec, m)
         name, n_chunks, single, multi = self._step_lists
         tensors = step.extras["tensors"]
         carry = decay = None
@@ -126,9 +122,11 @@ class MatrixMemory(Mixer):
             carry = ws.get("mlstm.carry", (n_chunks, H, D, Dv + 1), f32, (most, H, D, Dv + 1))
             decay = ws.get("mlstm.decay", (n_chunks, H, D), f32, (most, H, D))
         o32 = ws.get("mlstm.o32", (T, H, Dv + 1), f32, (cap, H, Dv + 1))
-        ops.gla_scan(q32, k32, v32, z, None, 1.0, D ** -0.5, cache.tensors["s"], step.state_slots, step.seg_info,
-                     len(step.segments), tensors[name], n_chunks, tensors[name + ".segments"], single, multi, carry,
-                     decay, o32)
+        # q, k, v where the projection left them; e^i on the keys, e^f as the head's decay, the normaliser's ones
+        ops.gla_scan(proj[:, : H * D], proj[:, H * D: 2 * H * D], proj[:, 2 * H * D: self.g_row], None, None, 1.0,
+                     D ** -0.5, cache.tensors["s"], step.state_slots, step.seg_info, len(step.segments), tensors[name],
+                     n_chunks, tensors[name + ".segments"], single, multi, carry, decay, o32, k_fac=kf, a_head=dec,
+                     ones_col=True)
         o = ws.get("mlstm.o", (T, H * Dv), dt, (cap, H * Dv))
         ops.mlstm_output(o32, m, proj[:, self.g_row:], self.params["norm.weight"], self.eps, o)
         out = ws.get("mlstm.out", (T, self.hidden), dt, (cap, self.hidden))

@@ -414,12 +414,20 @@ def gated_heads(x, gates, out, dim, act="sigmoid", norm_weight=None, eps=0.0):
 
 
 def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, seg_info, n_segs, chunks, n_chunks, seg_chunks,
-             any_single, any_multi, carry, decay_prod, out):
+             any_single, any_multi, carry, decay_prod, out, k_fac=None, a_head=None, ones_col=False):
     """Token by token from each request's slot; the chunk lists only steer how the kernel shares the work."""
     H, D, Dv = state.shape[1:]
-    zz = z.float() + (z_bias.float().view(1, -1) if z_bias is not None else 0.0)
-    decay = torch.exp(-torch.nn.functional.softplus(-zz) / tau).view(-1, H, D)
-    qq, kk, vv = q.float().view(-1, H, D) * q_scale, k.float().view(-1, H, D), v.float().view(-1, H, Dv)
+    if a_head is not None:
+        decay = a_head.float()[:, :, None].expand(-1, H, D)
+    else:
+        zz = z.float() + (z_bias.float().view(1, -1) if z_bias is not None else 0.0)
+        decay = torch.exp(-torch.nn.functional.softplus(-zz) / tau).view(-1, H, D)
+    qq, kk = q.float().view(-1, H, D) * q_scale, k.float().view(-1, H, D)
+    if k_fac is not None:
+        kk = kk * k_fac.float()[:, :, None]
+    vv = v.float().view(-1, H, Dv - (1 if ones_col else 0))
+    if ones_col:
+        vv = torch.cat([vv, torch.ones(vv.shape[0], H, 1)], dim=-1)
     for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
         slot = int(state_slots[i])
         S = torch.zeros(H, D, Dv) if kv_len == q_len else state[slot].clone()
@@ -507,13 +515,13 @@ def latent_query_rotate(q, flat_dim, rot_dim, n_rot, interleaved, positions, rop
                                                        interleaved).to(q_out.dtype)
 
 
-def mlstm_gates(pre, bias_i, bias_f, cap, m_state, state_slots, seg_info, n_segs, gate_i, logit_f, m_out):
+def mlstm_gates(pre, bias_i, bias_f, cap, m_state, state_slots, seg_info, n_segs, key_fac, decay, m_out):
     H = pre.shape[1] // 2
     gi = cap * torch.tanh((pre[:, :H].float() + bias_i.float()) / cap)
     zf = cap * torch.tanh((pre[:, H:].float() + bias_f.float()) / cap)
-    gate_i.copy_(gi)
-    logit_f.copy_(zf)
     f = torch.nn.functional.logsigmoid(zf)
+    key_fac.copy_(torch.exp(gi))
+    decay.copy_(torch.exp(f))
     for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
         slot = int(state_slots[i])
         m = torch.zeros(H) if kv_len == q_len else m_state[slot].clone()
@@ -521,16 +529,6 @@ def mlstm_gates(pre, bias_i, bias_f, cap, m_state, state_slots, seg_info, n_segs
             m = torch.maximum(f[t] + m, gi[t])
             m_out[t] = m
         m_state[slot] = m
-
-
-def mlstm_prepare(proj, n_heads, dim, vdim, gate_i, logit_f, q32, k32, v32, z):
-    T, H = proj.shape[0], n_heads
-    p = proj.float()
-    q32.copy_(p[:, :H * dim])
-    k32.copy_((torch.exp(gate_i)[:, :, None] * p[:, H * dim:2 * H * dim].view(T, H, dim)).view(T, -1))
-    v = p[:, 2 * H * dim:2 * H * dim + H * vdim].view(T, H, vdim)
-    v32.copy_(torch.cat([v, torch.ones(T, H, 1)], dim=-1).view(T, -1))
-    z.copy_(logit_f[:, :, None].expand(T, H, dim).reshape(T, -1))
 
 
 def mlstm_output(o32, m, gates, norm_weight, eps, out):
@@ -542,7 +540,7 @@ def mlstm_output(o32, m, gates, norm_weight, eps, out):
     out.copy_(y.to(out.dtype))
 
 
-ALL = ["short_conv", "depth_mix", "moe_gather_scaled", "relu2_", "latent_store", "latent_query_rotate", "mlstm_gates", "mlstm_prepare", "mlstm_output", "linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+ALL = ["short_conv", "depth_mix", "moe_gather_scaled", "relu2_", "latent_store", "latent_query_rotate", "mlstm_gates", "mlstm_output", "linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gemm1_gather_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 

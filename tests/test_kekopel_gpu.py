@@ -315,18 +315,16 @@ def test_matrix_memory_kernels_against_the_stated_recurrence(dtype, H, D, Dv, ca
     m0 = rnd(len(lens) + 1, H, seed=7)
     state, m_state = S0.clone(), m0.clone()
     f32 = dict(dtype=torch.float32, device=DEV)
-    gi, zf, m = torch.zeros(T, H, **f32), torch.zeros(T, H, **f32), torch.zeros(T, H, **f32)
-    ops.mlstm_gates(pre, bi, bf, cap, m_state, slots, info, len(lens), gi, zf, m)
-    q32, k32, z = torch.zeros(T, H * D, **f32), torch.zeros(T, H * D, **f32), torch.zeros(T, H * D, **f32)
-    v32 = torch.zeros(T, H * (Dv + 1), **f32)
-    ops.mlstm_prepare(proj, H, D, Dv, gi, zf, q32, k32, v32, z)
+    kf, dec, m = torch.zeros(T, H, **f32), torch.zeros(T, H, **f32), torch.zeros(T, H, **f32)
+    ops.mlstm_gates(pre, bi, bf, cap, m_state, slots, info, len(lens), kf, dec, m)
     chunks, per_seg, single, multi = chunk_list(lens, 64)
     n_chunks = chunks.shape[0]
     carry = torch.zeros(n_chunks, H, D, Dv + 1, **f32)
     decay = torch.zeros(n_chunks, H, D, **f32)
     o32 = torch.zeros(T, H, Dv + 1, **f32)
-    ops.gla_scan(q32, k32, v32, z, None, 1.0, D ** -0.5, state, slots, info, len(lens), torch.from_numpy(chunks).to(DEV),
-                 n_chunks, torch.from_numpy(per_seg).to(DEV), single, multi, carry, decay, o32)
+    ops.gla_scan(proj[:, :H * D], proj[:, H * D:2 * H * D], proj[:, 2 * H * D:H * (2 * D + Dv)], None, None, 1.0, D ** -0.5,
+                 state, slots, info, len(lens), torch.from_numpy(chunks).to(DEV), n_chunks,
+                 torch.from_numpy(per_seg).to(DEV), single, multi, carry, decay, o32, k_fac=kf, a_head=dec, ones_col=True)
     out = torch.zeros(T, H * Dv, dtype=dtype, device=DEV)
     gates = proj[:, H * (2 * D + Dv):]
     ops.mlstm_output(o32, m, gates, w, 1e-5, out)
