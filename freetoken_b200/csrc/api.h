@@ -125,13 +125,14 @@ int ftk_gated_heads(const void* x, int x_f32, int x_stride, const void* gates, l
 // of several chunks.  out [T, H, vdim] float32.  z [T, H * dim] float32 holds the decay logits and is overwritten
 // (with the decays) when a segment has several chunks.  k_fac [T, H] (or null) multiplies a token's keys per head,
 // in 32 bits; a_head [T, H] (or null) gives one decay per (token, head) in place of z; with ones_col = 1 the last of
-// the vdim value columns is 1 for every token and v holds vdim - 1 columns per head.
+// the vdim value columns is 1 for every token and v holds vdim - 1 columns per head; with out_ones [T, H] that
+// column's outputs go there and out is [T, H, vdim - 1].
 int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
                  long long v_stride, int dtype, float* z, const float* z_bias, float tau, float q_scale,
                  float* state, int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs,
                  const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, int any_single, int any_multi,
                  float* carry, float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
-                 const float* k_fac, const float* a_head, int ones_col, void* stream);
+                 const float* k_fac, const float* a_head, int ones_col, float* out_ones, void* stream);
 // Short causal convolution over time with a residual (shortconv.cu): out[t, c] = x[t, c] + sum_j w[c, j] *
 // in(t - taps + 1 + j, c) over the request's own inputs; the last taps - 1 inputs of every request live in its
 // state slot (state [n_slots, taps - 1, channels] float32, oldest first; zeros before the sequence's start) and are
@@ -164,8 +165,8 @@ int ftk_latent_query_rotate(const void* q, int dtype, int n_heads, int flat_dim,
 int ftk_mlstm_gates(const float* pre, const float* bias_i, const float* bias_f, float cap, float* m_state, int n_slots,
                     const int32_t* state_slots, const int32_t* seg_info, int n_segs, int n_heads, int n_tokens,
                     float* key_fac, float* decay, float* m_out, void* stream);
-// o32 [T, heads, vdim + 1] (the last column is n . q); out [T, heads * vdim] of `dtype`.
-int ftk_mlstm_output(const float* o32, const float* m, const void* gates, long long gate_stride, const float* norm_w,
+// o32 [T, heads, vdim], nq [T, heads] (n . q); out [T, heads * vdim] of `dtype`.
+int ftk_mlstm_output(const float* o32, const float* nq, const float* m, const void* gates, long long gate_stride, const float* norm_w,
                      float eps, void* out, int dtype, int n_tokens, int n_heads, int vdim, void* stream);
 int ftk_act_and_mul(const void* gate_up, int dtype, int n_rows, int inter, int act, float alpha,
                     float limit, void* out, void* stream);

@@ -10,7 +10,7 @@
 // under the change of scale.  Two kernels around the recurrence kernel, which reads q, k and v where the projection
 // left them, multiplies the keys by e^(i_t) in 32 bits as it stages them, takes e^(f_t) as the head's decay and adds
 // the column of ones itself:
-//   gates    per (request, head), a warp: e^(i_t), e^(f_t) and m_t of the step's tokens (two warp scans per 32 tokens:
+//   gates    per (request, head), a warp: e^(i_t), e^(f_t) and m_t of the step's tokens (two warp scans per 128 tokens, four consecutive tokens a lane:
 //            F_t = f_1 + ... + f_t, m_t = F_t + max(m_0, max_(s <= t) (i_s - F_s))), m left in the request's slot;
 //   output   per (token, head): the division, the head's unit norm, the weight, the sigmoid gate.
 #include "common.cuh"
@@ -35,52 +35,85 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, const float* _
   const int slot = state_slots[seg];
   const bool has_slot = slot >= 0 && slot < n_slots;
   float m = (has_slot && kv_len > q_len) ? m_state[(size_t)slot * H + h] : 0.f;
-  for (int t0 = 0; t0 < q_len; t0 += 32) {
-    const int t = t0 + lane;
-    const bool on = t < q_len;
-    float gi = -INFINITY, f = 0.f;
-    if (on) {
-      const float* row = pre + (size_t)(q_start + t) * 2 * H;
-      gi = capped(row[h] + bias_i[h], cap);
-      f = log_sigmoid(capped(row[H + h] + bias_f[h], cap));
+  constexpr int K = 4;  // tokens per lane and pass (consecutive ones): their loads are in flight together
+  for (int t0 = 0; t0 < q_len; t0 += 32 * K) {
+    float gi[K], F[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int t = t0 + lane * K + j;
+      gi[j] = -INFINITY;
+      F[j] = 0.f;
+      if (t < q_len) {
+        const float* row = pre + (size_t)(q_start + t) * 2 * H;
+        gi[j] = row[h] + bias_i[h];
+        F[j] = row[H + h] + bias_f[h];
+      }
     }
-    float F = f;  // inclusive sum of the forget gates over the lanes
+    float e_f[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const bool on = t0 + lane * K + j < q_len;
+      gi[j] = on ? capped(gi[j], cap) : -INFINITY;
+      const float f = on ? log_sigmoid(capped(F[j], cap)) : 0.f;
+      e_f[j] = expf(f);
+      F[j] = f + (j ? F[j - 1] : 0.f);  // the sum of the forget gates within the lane
+    }
+    float tot = F[K - 1], before = tot;  // over the lanes: inclusive, then what lies in front of this lane
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const float v = __shfl_up_sync(0xffffffffu, F, o);
-      if (lane >= o) F += v;
+      const float v = __shfl_up_sync(0xffffffffu, before, o);
+      if (lane >= o) before += v;
     }
-    float best = on ? gi - F : -INFINITY;  // inclusive maximum of i_s - F_s
+    before -= tot;
+    float best[K];  // the maximum of i_s - F_s up to each token, within the lane
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      F[j] += before;
+      best[j] = gi[j] - F[j];
+      if (j) best[j] = fmaxf(best[j], best[j - 1]);
+    }
+    float upto = best[K - 1];  // over the lanes, inclusive
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const float v = __shfl_up_sync(0xffffffffu, best, o);
-      if (lane >= o) best = fmaxf(best, v);
+      const float v = __shfl_up_sync(0xffffffffu, upto, o);
+      if (lane >= o) upto = fmaxf(upto, v);
     }
-    const float mt = F + fmaxf(m, best);
-    if (on) {
-      const size_t at = (size_t)(q_start + t) * H + h;
-      key_fac[at] = expf(gi);
-      decay[at] = expf(f);
-      m_out[at] = mt;
+    float front = __shfl_up_sync(0xffffffffu, upto, 1);
+    if (lane == 0) front = -INFINITY;
+    float mt[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int t = t0 + lane * K + j;
+      mt[j] = F[j] + fmaxf(m, fmaxf(front, best[j]));
+      if (t < q_len) {
+        const size_t at = (size_t)(q_start + t) * H + h;
+        key_fac[at] = expf(gi[j]);
+        decay[at] = e_f[j];
+        m_out[at] = mt[j];
+      }
     }
-    const int last = min(31, q_len - t0 - 1);
-    m = __shfl_sync(0xffffffffu, mt, last);
+    const int last = min(32 * K - 1, q_len - t0 - 1);
+    float mine = mt[0];
+#pragma unroll
+    for (int j = 1; j < K; ++j)
+      if (j == last % K) mine = mt[j];
+    m = __shfl_sync(0xffffffffu, mine, last / K);
   }
   if (has_slot && lane == 0) m_state[(size_t)slot * H + h] = m;
 }
 
 // a warp per (token, head)
 template <typename T>
-__global__ void mlstm_output_kernel(const float* __restrict__ o32, const float* __restrict__ m, const T* __restrict__ gates,
-                                    long long gate_stride, const float* __restrict__ norm_w, float eps, T* __restrict__ out,
-                                    int n_tokens, int H, int Dv) {
+__global__ void mlstm_output_kernel(const float* __restrict__ o32, const float* __restrict__ nq, const float* __restrict__ m,
+                                    const T* __restrict__ gates, long long gate_stride, const float* __restrict__ norm_w,
+                                    float eps, T* __restrict__ out, int n_tokens, int H, int Dv) {
   pdl_wait();
   pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n_tokens * H) return;
   const int t = warp / H, h = warp - t * H;
-  const float* src = o32 + ((size_t)t * H + h) * (Dv + 1);
-  const float den = fmaxf(fabsf(src[Dv]), 1.f) + 1e-6f * expf(m[(size_t)t * H + h]);
+  const float* src = o32 + ((size_t)t * H + h) * Dv;
+  const float den = fmaxf(fabsf(nq[(size_t)t * H + h]), 1.f) + 1e-6f * expf(m[(size_t)t * H + h]);
   float ss = 0.f;
   for (int d = lane; d < Dv; d += 32) {
     const float v = src[d] / den;
@@ -95,6 +128,49 @@ __global__ void mlstm_output_kernel(const float* __restrict__ o32, const float* 
     const float gate = 1.f / (1.f + expf(-to_float(g[d])));
     dst[d] = from_float<T>(v * gate);
   }
+}
+
+// The same for bfloat16 heads of 8 x 2^k values (k <= 5) whose rows allow 16-byte accesses: a thread takes eight
+// consecutive values, the TPR threads of a (token, head) sit side by side in a warp and add their squares by shuffles.
+template <int TPR>
+__global__ void __launch_bounds__(256) mlstm_output_vec_kernel(const float* __restrict__ o32, const float* __restrict__ nq,
+                                                               const float* __restrict__ m,
+                                                               const __nv_bfloat16* __restrict__ gates, long long gate_stride,
+                                                               const float* __restrict__ norm_w, float eps,
+                                                               __nv_bfloat16* __restrict__ out, int n_tokens, int H) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int Dv = TPR * 8;
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / TPR;
+  const int d = (threadIdx.x % TPR) * 8;
+  const bool ok = w < (long long)n_tokens * H;
+  const long long wr = ok ? w : 0;
+  const long long t = wr / H;
+  const int h = (int)(wr % H);
+  const float* src = o32 + (size_t)wr * Dv + d;
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  const uint4 graw = *reinterpret_cast<const uint4*>(gates + t * gate_stride + (size_t)h * Dv + d);
+  const float4 w0 = *reinterpret_cast<const float4*>(norm_w + h * Dv + d), w1 = *reinterpret_cast<const float4*>(norm_w + h * Dv + d + 4);
+  const float den = fmaxf(fabsf(nq[wr]), 1.f) + 1e-6f * expf(m[wr]);
+  float v[8] = {a.x / den, a.y / den, a.z / den, a.w / den, b.x / den, b.y / den, b.z / den, b.w / den};
+  const float wt[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) ss += v[u] * v[u];
+#pragma unroll
+  for (int o = TPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = rsqrtf(ss / (float)Dv + eps);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+  uint4 res;
+  __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const float2 g = __bfloat1622float2(g2[u]);
+    const float y0 = v[2 * u] * r * wt[2 * u] / (1.f + expf(-g.x));
+    const float y1 = v[2 * u + 1] * r * wt[2 * u + 1] / (1.f + expf(-g.y));
+    r2[u] = __floats2bfloat162_rn(y0, y1);
+  }
+  if (ok) *reinterpret_cast<uint4*>(out + (size_t)wr * Dv + d) = res;
 }
 
 }  // namespace ftk
@@ -115,20 +191,32 @@ extern "C" int ftk_mlstm_gates(const float* pre, const float* bias_i, const floa
   return 0;
 }
 
-extern "C" int ftk_mlstm_output(const float* o32, const float* m, const void* gates, long long gate_stride,
+extern "C" int ftk_mlstm_output(const float* o32, const float* nq, const float* m, const void* gates, long long gate_stride,
                                 const float* norm_w, float eps, void* out, int dtype, int n_tokens, int n_heads, int vdim,
                                 void* stream) {
   FTK_REQUIRE(dtype_ok(dtype) && n_heads >= 1 && vdim >= 1 && n_tokens >= 0, "mlstm_output: bad arguments");
   if (n_tokens == 0) return 0;
-  FTK_REQUIRE(o32 && m && gates && norm_w && out, "mlstm_output: null pointer");
+  FTK_REQUIRE(o32 && nq && m && gates && norm_w && out, "mlstm_output: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
   const long long warps = (long long)n_tokens * n_heads;
+  const int tpr = vdim / 8;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (dtype == FTK_BF16 && vdim % 8 == 0 && tpr <= 32 && (tpr & (tpr - 1)) == 0 && gate_stride % 8 == 0 && al16(o32) &&
+      al16(gates) && al16(norm_w) && al16(out)) {
+    const unsigned blocks = (unsigned)((warps * tpr + 255) / 256);
+#define FTK_MO(N) FTK_LAUNCH(mlstm_output_vec_kernel<N>, blocks, 256, 0, s, o32, nq, m, (const __nv_bfloat16*)gates, gate_stride, \
+                             norm_w, eps, (__nv_bfloat16*)out, n_tokens, n_heads)
+    (tpr == 1 ? FTK_MO(1) : tpr == 2 ? FTK_MO(2) : tpr == 4 ? FTK_MO(4) : tpr == 8 ? FTK_MO(8) : tpr == 16 ? FTK_MO(16) : FTK_MO(32));
+#undef FTK_MO
+    FTK_LAUNCH_CHECK("mlstm_output");
+    return 0;
+  }
   const unsigned blocks = (unsigned)((warps + 3) / 4);
   if (dtype == FTK_F32)
-    FTK_LAUNCH(mlstm_output_kernel<float>, blocks, 128, 0, s, o32, m, (const float*)gates, gate_stride, norm_w, eps, (float*)out,
+    FTK_LAUNCH(mlstm_output_kernel<float>, blocks, 128, 0, s, o32, nq, m, (const float*)gates, gate_stride, norm_w, eps, (float*)out,
                n_tokens, n_heads, vdim);
   else
-    FTK_LAUNCH(mlstm_output_kernel<__nv_bfloat16>, blocks, 128, 0, s, o32, m, (const __nv_bfloat16*)gates, gate_stride, norm_w,
+    FTK_LAUNCH(mlstm_output_kernel<__nv_bfloat16>, blocks, 128, 0, s, o32, nq, m, (const __nv_bfloat16*)gates, gate_stride, norm_w,
                eps, (__nv_bfloat16*)out, n_tokens, n_heads, vdim);
   FTK_LAUNCH_CHECK("mlstm_output");
   return 0;

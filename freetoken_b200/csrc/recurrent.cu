@@ -54,6 +54,7 @@ struct GlaArgs {
   const float* k_fac;      // [T, H] or null: a factor on token t's keys of head h (applied in 32 bits while they are staged)
   const float* a_head;     // [T, H] or null: one decay per (token, head) for all key channels, in place of z
   int ones_col;            // 1: the last of the Dv value columns is 1 for every token, and v holds Dv - 1 columns per head
+  float* out_ones;         // [T, H] or null: with ones_col, that column's outputs go here and out is [T, H, Dv - 1]
 };
 
 // 16 bytes from global to shared memory without a trip through registers; `valid` false writes zeros
@@ -343,7 +344,10 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
           float o = 0.f;
 #pragma unroll
           for (int w = 0; w < kGlaSlices; ++w) o += part[(w * kGlaBatch + t) * cols + j];  // slices in order
-          a.out[((size_t)(q_start + tok0 + b0 + t) * a.H + h) * Dv + col0 + j] = o;
+          const size_t row = (size_t)(q_start + tok0 + b0 + t) * a.H + h;
+          if (!a.out_ones) a.out[row * Dv + col0 + j] = o;
+          else if (col0 + j == Dvin) a.out_ones[row] = o;
+          else a.out[row * Dvin + col0 + j] = o;
         }
       }
     }
@@ -444,7 +448,7 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
                             const int32_t* seg_info, int n_segs, const int32_t* chunks, int n_chunks,
                             const int32_t* seg_chunks, int any_single, int any_multi, float* carry,
                             float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
-                            const float* k_fac, const float* a_head, int ones_col, void* stream) {
+                            const float* k_fac, const float* a_head, int ones_col, float* out_ones, void* stream) {
   FTK_REQUIRE(dtype_ok(dtype), "gla_scan: bad dtype %d", dtype);
   FTK_REQUIRE(n_tokens >= 0 && n_segs >= 0 && n_chunks >= 0, "gla_scan: bad counts");
   if (n_tokens == 0 || n_chunks == 0) return 0;
@@ -462,7 +466,8 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
   a.z = z; a.z_bias = z_bias; a.z_is_decay = 0; a.groups = 1; a.inv_tau = 1.f / tau; a.q_scale = q_scale;
   a.state = state; a.state_slots = state_slots; a.seg_info = seg_info; a.chunks = chunks; a.seg_chunks = seg_chunks;
   a.n_chunks = n_chunks; a.n_segs = n_segs; a.n_slots = n_slots; a.carry = carry; a.decay_prod = decay_prod;
-  a.k_fac = k_fac; a.a_head = a_head; a.ones_col = ones_col;
+  FTK_REQUIRE(!out_ones || ones_col, "gla_scan: outputs of a column of ones that is not there");
+  a.k_fac = k_fac; a.a_head = a_head; a.ones_col = ones_col; a.out_ones = out_ones;
   a.out = out; a.H = n_heads; a.D = dim; a.Dv = vdim; a.n_tokens = n_tokens;
   cudaStream_t s = (cudaStream_t)stream;
   note_variant(any_multi ? "gla_scan: chunks side by side" : "gla_scan: one chunk per request");

@@ -367,18 +367,18 @@ def bench_kekopel(a) -> dict:
     state = torch.zeros(n_slots, H, D, Dv + 1, device=dev)
     carry = torch.empty(n, H, D, Dv + 1, device=dev) if multi else None
     decay = torch.empty(n, H, D, device=dev) if multi else None
-    o32 = torch.empty(T, H, Dv + 1, device=dev)
+    o32, nq = torch.empty(T, H, Dv, device=dev), torch.empty(T, H, device=dev)
     cd, pd = torch.from_numpy(chunks).to(dev), torch.from_numpy(per_seg).to(dev)
     passes = 2 if multi else 1
     add("gla_scan (a key factor and a decay per head, the normaliser as a column of ones)",
         lambda: ops.gla_scan(wide[:, :H * D], wide[:, H * D:2 * H * D], wide[:, 2 * H * D:H * (2 * D + Dv)], None, None, 1.0,
                              D ** -0.5, state, slots, seg, len(segs), cd, n, pd, single, multi, carry, decay, o32,
-                             k_fac=gi, a_head=zf, ones_col=True),
+                             k_fac=gi, a_head=zf, ones_col=True, out_ones=nq),
         T * H * ((2 * D + Dv) * 2 + 8) * passes + T * H * (Dv + 1) * 4 + (2 * len(segs) + (2 * n if multi else 0)) * H * D * (Dv + 1) * 4,
         T * H * D * (Dv + 1) * (8 if multi else 5))
     o = torch.empty(T, H * Dv, dtype=bf, device=dev)
     nw = torch.ones(H * Dv, device=dev)
-    add("mlstm_output", lambda: ops.mlstm_output(o32, m, wide[:, H * (2 * D + Dv):], nw, 1e-6, o),
+    add("mlstm_output", lambda: ops.mlstm_output(o32, nq, m, wide[:, H * (2 * D + Dv):], nw, 1e-6, o),
         T * H * ((Dv + 1) * 4 + 4 + Dv * 2 * 2))
     results["status"] = ops.read_status()
     return results

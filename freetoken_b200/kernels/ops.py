@@ -143,9 +143,9 @@ _SIGNATURES = {
                          ctypes.c_longlong, _vp, _i, _i, _vp],
     "ftk_latent_query_rotate": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "ftk_mlstm_gates": [_vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
-    "ftk_mlstm_output": [_vp, _vp, _vp, ctypes.c_longlong, _vp, _f, _vp, _i, _i, _i, _i, _vp],
+    "ftk_mlstm_output": [_vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "ftk_gla_scan": [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _i, _vp, _vp, _f, _f,
-                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp],
+                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
 }
 _bound = False
 _launches = 0
@@ -1072,7 +1072,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
              n_segs: int, chunks: torch.Tensor, n_chunks: int, seg_chunks: torch.Tensor, any_single: bool,
              any_multi: bool, carry: Optional[torch.Tensor], decay_prod: Optional[torch.Tensor],
              out: torch.Tensor, k_fac: Optional[torch.Tensor] = None, a_head: Optional[torch.Tensor] = None,
-             ones_col: bool = False) -> None:
+             ones_col: bool = False, out_ones: Optional[torch.Tensor] = None) -> None:
     """Gated linear attention of the step's tokens, per (request, head):
     ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t q_scale)``, ``a_t = sigmoid(z_t + z_bias)^(1 / tau)``.
 
@@ -1086,13 +1086,16 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     ``k_fac [T, H]`` float32 multiplies a token's keys of a head (in 32 bits, as they are read); ``a_head [T, H]``
     float32 gives one decay per (token, head) for all key channels, and ``z`` is then ``None``; with ``ones_col``
     the state's last value column belongs to a value that is 1 for every token, and ``v`` is ``[T, H * (Dv - 1)]``
-    (the sum of the keys under the same decays: a normaliser)."""
+    (the sum of the keys under the same decays: a normaliser); with ``out_ones [T, H]`` that column's outputs go
+    there and ``out`` is ``[T, H, Dv - 1]``."""
     T = out.shape[0]
     H, D, Dv = state.shape[1], state.shape[2], state.shape[3]
     if q.shape != (T, H * D) or k.shape != (T, H * D) or v.shape != (T, H * (Dv - (1 if ones_col else 0))) \
-            or out.shape != (T, H, Dv) or (z is None) == (a_head is None) or (z is not None and z.shape != (T, H * D)):
+            or out.shape != (T, H, Dv - (1 if out_ones is not None else 0)) or (z is None) == (a_head is None) or (z is not None and z.shape != (T, H * D)):
         raise KernelError("gla_scan: shapes do not agree")
-    for name, f in (("k_fac", k_fac), ("a_head", a_head)):
+    if out_ones is not None and not ones_col:
+        raise KernelError("gla_scan: out_ones goes with ones_col")
+    for name, f in (("k_fac", k_fac), ("a_head", a_head), ("out_ones", out_ones)):
         if f is not None and (f.shape != (T, H) or not f.is_contiguous()):
             raise KernelError(f"gla_scan: {name} must be a contiguous [T, H]")
     if q.dtype != k.dtype or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
@@ -1113,7 +1116,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         _dev(seg_chunks, "seg_chunks", torch.int32), 1 if any_single else 0, 1 if any_multi else 0,
         _dev(carry, "carry", torch.float32), _dev(decay_prod, "decay_prod", torch.float32),
         _dev(out, "out", torch.float32), T, H, D, Dv, _dev(k_fac, "k_fac", torch.float32),
-        _dev(a_head, "a_head", torch.float32), 1 if ones_col else 0, _stream()), "gla_scan", max(1, launches))
+        _dev(a_head, "a_head", torch.float32), 1 if ones_col else 0, _dev(out_ones, "out_ones", torch.float32),
+        _stream()), "gla_scan", max(1, launches))
 
 
 # --------------------------------------------------------------------------- short convolution, depth mix
@@ -1242,17 +1246,16 @@ def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, c
         _dev(m_out, "m_out", torch.float32), _stream()), "mlstm_gates")
 
 
-def mlstm_output(o32: torch.Tensor, m: torch.Tensor, gates: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                 out: torch.Tensor) -> None:
-    """``o32 [T, H, vdim + 1]`` (numerator columns and ``n . q``), ``m [T, H]``: ``o = num / (max(|n . q|, 1) +
+def mlstm_output(o32: torch.Tensor, nq: torch.Tensor, m: torch.Tensor, gates: torch.Tensor, norm_weight: torch.Tensor,
+                 eps: float, out: torch.Tensor) -> None:
+    """``o32 [T, H, vdim]`` (numerators), ``nq [T, H]`` (``n . q``), ``m [T, H]``: ``o = num / (max(|n . q|, 1) +
     1e-6 e^m)``, divided by its root mean square over the head, times ``norm_weight [H * vdim]``, times
     ``sigmoid(gates)`` (``gates [T, H * vdim]``, a view of adjacent columns is fine) into ``out [T, H * vdim]``."""
-    T, H, dv1 = o32.shape
-    Dv = dv1 - 1
+    T, H, Dv = o32.shape
     if out.shape != (T, H * Dv) or gates.shape != (T, H * Dv) or gates.stride(1) != 1 or gates.dtype != out.dtype \
-            or norm_weight.numel() != H * Dv or m.shape != (T, H) or not out.is_contiguous():
+            or norm_weight.numel() != H * Dv or m.shape != (T, H) or nq.shape != (T, H) or not out.is_contiguous():
         raise KernelError("mlstm_output: shapes or dtypes do not agree")
     _check(_lib().ftk_mlstm_output(
-        _dev(o32, "o32", torch.float32), _dev(m, "m", torch.float32), gates.data_ptr(),
+        _dev(o32, "o32", torch.float32), _dev(nq, "nq", torch.float32), _dev(m, "m", torch.float32), gates.data_ptr(),
         gates.stride(0) if T > 1 else H * Dv, _dev(norm_weight, "norm_weight", torch.float32), float(eps),
         _dev(out, "out"), _code(out, "out"), T, H, Dv, _stream()), "mlstm_output")

@@ -121,14 +121,15 @@ class MatrixMemory(Mixer):
             most = self.max_chunks(cap)
             carry = ws.get("mlstm.carry", (n_chunks, H, D, Dv + 1), f32, (most, H, D, Dv + 1))
             decay = ws.get("mlstm.decay", (n_chunks, H, D), f32, (most, H, D))
-        o32 = ws.get("mlstm.o32", (T, H, Dv + 1), f32, (cap, H, Dv + 1))
+        o32 = ws.get("mlstm.o32", (T, H, Dv), f32, (cap, H, Dv))
+        nq = ws.get("mlstm.nq", (T, H), f32, (cap, H))
         # q, k, v where the projection left them; e^i on the keys, e^f as the head's decay, the normaliser's ones
         ops.gla_scan(proj[:, : H * D], proj[:, H * D: 2 * H * D], proj[:, 2 * H * D: self.g_row], None, None, 1.0,
                      D ** -0.5, cache.tensors["s"], step.state_slots, step.seg_info, len(step.segments), tensors[name],
                      n_chunks, tensors[name + ".segments"], single, multi, carry, decay, o32, k_fac=kf, a_head=dec,
-                     ones_col=True)
+                     ones_col=True, out_ones=nq)
         o = ws.get("mlstm.o", (T, H * Dv), dt, (cap, H * Dv))
-        ops.mlstm_output(o32, m, proj[:, self.g_row:], self.params["norm.weight"], self.eps, o)
+        ops.mlstm_output(o32, nq, m, proj[:, self.g_row:], self.params["norm.weight"], self.eps, o)
         out = ws.get("mlstm.out", (T, self.hidden), dt, (cap, self.hidden))
         ops.linear(o, self.params["o_proj.weight"], out)
         return out

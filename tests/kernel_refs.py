@@ -414,7 +414,7 @@ def gated_heads(x, gates, out, dim, act="sigmoid", norm_weight=None, eps=0.0):
 
 
 def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, seg_info, n_segs, chunks, n_chunks, seg_chunks,
-             any_single, any_multi, carry, decay_prod, out, k_fac=None, a_head=None, ones_col=False):
+             any_single, any_multi, carry, decay_prod, out, k_fac=None, a_head=None, ones_col=False, out_ones=None):
     """Token by token from each request's slot; the chunk lists only steer how the kernel shares the work."""
     H, D, Dv = state.shape[1:]
     if a_head is not None:
@@ -433,7 +433,11 @@ def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, seg_info, n_s
         S = torch.zeros(H, D, Dv) if kv_len == q_len else state[slot].clone()
         for t in range(q_start, q_start + q_len):
             S = decay[t][:, :, None] * S + kk[t][:, :, None] * vv[t][:, None, :]
-            out[t] = torch.einsum("hdv,hd->hv", S, qq[t])
+            o = torch.einsum("hdv,hd->hv", S, qq[t])
+            if out_ones is None:
+                out[t] = o
+            else:
+                out[t], out_ones[t] = o[:, :-1], o[:, -1]
         state[slot] = S
 
 
@@ -531,10 +535,9 @@ def mlstm_gates(pre, bias_i, bias_f, cap, m_state, state_slots, seg_info, n_segs
         m_state[slot] = m
 
 
-def mlstm_output(o32, m, gates, norm_weight, eps, out):
-    T, H, dv1 = o32.shape
-    Dv = dv1 - 1
-    o = o32[:, :, :Dv] / (torch.clamp(o32[:, :, Dv:].abs(), min=1.0) + 1e-6 * torch.exp(m)[:, :, None])
+def mlstm_output(o32, nq, m, gates, norm_weight, eps, out):
+    T, H, Dv = o32.shape
+    o = o32 / (torch.clamp(nq.abs(), min=1.0) + 1e-6 * torch.exp(m))[:, :, None]
     o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)
     y = o.reshape(T, H * Dv) * norm_weight.float() * torch.sigmoid(gates.float())
     out.copy_(y.to(out.dtype))

@@ -321,13 +321,14 @@ def test_matrix_memory_kernels_against_the_stated_recurrence(dtype, H, D, Dv, ca
     n_chunks = chunks.shape[0]
     carry = torch.zeros(n_chunks, H, D, Dv + 1, **f32)
     decay = torch.zeros(n_chunks, H, D, **f32)
-    o32 = torch.zeros(T, H, Dv + 1, **f32)
+    o32, nq = torch.zeros(T, H, Dv, **f32), torch.zeros(T, H, **f32)
     ops.gla_scan(proj[:, :H * D], proj[:, H * D:2 * H * D], proj[:, 2 * H * D:H * (2 * D + Dv)], None, None, 1.0, D ** -0.5,
                  state, slots, info, len(lens), torch.from_numpy(chunks).to(DEV), n_chunks,
-                 torch.from_numpy(per_seg).to(DEV), single, multi, carry, decay, o32, k_fac=kf, a_head=dec, ones_col=True)
+                 torch.from_numpy(per_seg).to(DEV), single, multi, carry, decay, o32, k_fac=kf, a_head=dec, ones_col=True,
+                 out_ones=nq)
     out = torch.zeros(T, H * Dv, dtype=dtype, device=DEV)
     gates = proj[:, H * (2 * D + Dv):]
-    ops.mlstm_output(o32, m, gates, w, 1e-5, out)
+    ops.mlstm_output(o32, nq, m, gates, w, 1e-5, out)
     # the stated recurrence, request by request
     p = proj.float().cpu().double()
     qq = p[:, :H * D].view(T, H, D) * D ** -0.5
@@ -350,6 +351,61 @@ def test_matrix_memory_kernels_against_the_stated_recurrence(dtype, H, D, Dv, ca
         S, n = S * torch.exp(mm)[:, None, None], n * torch.exp(mm)[:, None]
         for got_s, want_s in ((state[i + 1, :, :, :Dv], S), (state[i + 1, :, :, Dv], n)):  # (relative to the largest entry)
             torch.testing.assert_close(got_s.cpu().double() / want_s.abs().max(), want_s / want_s.abs().max(), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("cuts", [[700], [333, 2, 365], [64, 64, 1, 1, 570], [699, 1]])
+def test_a_memory_written_once_is_read_hundreds_of_tokens_later(cuts):
+    """One token writes a value under a key that no later token uses, with its input gate open and every later one nearly
+    shut, and the forget gate stays open: 700 tokens and many chunks later a query along that key reads that value back,
+    however the tokens are cut into steps (the state and the maximum go through the slot).  Without the far token the
+    output would be another one altogether."""
+    H, D, Dv, cap, T = 2, 16, 24, 15.0, 700
+    f32 = dict(dtype=torch.float32, device=DEV)
+    g = torch.Generator().manual_seed(5)
+    k = torch.randn(T, H, D, generator=g) * 0.3
+    k[:, :, 0] = 0.0            # nobody but the first token writes along key channel 0
+    k[0] = 0.0
+    k[0, :, 0] = 4.0
+    v = torch.randn(T, H, Dv, generator=g)
+    q = torch.randn(T, H, D, generator=g) * 0.3
+    q[-1] = 0.0
+    q[-1, :, 0] = 4.0           # the last token asks along channel 0
+    gate = torch.zeros(T, H * Dv)
+    proj = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), gate], 1).to(DEV)
+    pre = torch.zeros(T, 2 * H)
+    pre[:, :H] = -2.0           # input gates: e^-2 for everyone ...
+    pre[0, :H] = 6.0            # ... but e^6 for the first token
+    pre[:, H:] = 40.0           # forget gates at the cap: logsigmoid(15), a few 1e-7 below 0
+    pre = pre.to(DEV)
+    zero, w = torch.zeros(H, device=DEV), torch.ones(H * Dv, device=DEV)
+    state, m_state = torch.zeros(2, H, D, Dv + 1, **f32), torch.zeros(2, H, **f32)
+    rows, t0 = [], 0
+    for n in cuts:
+        info, slots, _ = segs([(n, t0 + n)])
+        kf, dec, m = (torch.zeros(n, H, **f32) for _ in range(3))
+        ops.mlstm_gates(pre[t0:t0 + n].contiguous(), zero, zero, cap, m_state, slots, info, 1, kf, dec, m)
+        chunks, per_seg, single, multi = chunk_list([(n, t0 + n)], 64)
+        nc = chunks.shape[0]
+        carry, decay = torch.zeros(nc, H, D, Dv + 1, **f32), torch.zeros(nc, H, D, **f32)
+        o32, nq = torch.zeros(n, H, Dv, **f32), torch.zeros(n, H, **f32)
+        pr = proj[t0:t0 + n]
+        ops.gla_scan(pr[:, :H * D], pr[:, H * D:2 * H * D], pr[:, 2 * H * D:H * (2 * D + Dv)], None, None, 1.0, D ** -0.5,
+                     state, slots, info, 1, torch.from_numpy(chunks).to(DEV), nc, torch.from_numpy(per_seg).to(DEV), single,
+                     multi, carry, decay, o32, k_fac=kf, a_head=dec, ones_col=True, out_ones=nq)
+        out = torch.zeros(n, H * Dv, **f32)
+        ops.mlstm_output(o32, nq, m, pr[:, H * (2 * D + Dv):], w, 1e-6, out)
+        rows.append(out.cpu())
+        t0 += n
+    got = torch.cat(rows)[-1].view(H, Dv).double()
+    gi = cap * torch.tanh(pre.cpu().double()[:, :H] / cap)
+    gf = torch.nn.functional.logsigmoid(cap * torch.tanh(pre.cpu().double()[:, H:] / cap))
+    z = torch.zeros
+    o, _, _, _ = plain_memory(q.double() * D ** -0.5, k.double(), v.double(), gi, gf, z(H).double(), z(H, D, Dv).double(),
+                              z(H, D).double())
+    want = o[-1] / torch.sqrt((o[-1] * o[-1]).mean(-1, keepdim=True) + 1e-6) * 0.5
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+    far = v[0].double() / torch.sqrt((v[0].double() ** 2).mean(-1, keepdim=True)) * 0.5  # the first token's value, unit norm, half open gate
+    torch.testing.assert_close(got, far, rtol=1e-3, atol=1e-3)
 
 
 def test_the_running_maximum_starts_at_zero_and_is_carried():
