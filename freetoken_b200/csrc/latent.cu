@@ -68,27 +68,63 @@ __global__ void latent_store_kernel(const T* __restrict__ proj, long long row_st
   }
 }
 
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store2(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float2 v) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+}
+
 template <typename T>
 __global__ void latent_query_rotate_kernel(const T* __restrict__ q, int n_heads, int flat_dim, int rot_dim, int n_rot,
                                            int interleaved, const int32_t* __restrict__ positions,
                                            const float* __restrict__ table, int max_pos, T* __restrict__ q_out,
-                                           int kv_rank, int pad_dim) {
+                                           int kv_rank, int pad_dim, int heads_per_block) {
   pdl_wait();
   pdl_trigger();
-  extern __shared__ float sm[];  // [n_heads][rot_dim]
-  const int t = blockIdx.x;
+  extern __shared__ float sm[];  // [heads of this block][rot_dim]
+  const int t = blockIdx.x, h0 = blockIdx.y * heads_per_block;
   const int qd = flat_dim + rot_dim;
-  const T* src = q + (size_t)t * n_heads * qd;
-  for (int i = threadIdx.x; i < n_heads * rot_dim; i += blockDim.x) {
-    const int h = i / rot_dim, d = i - h * rot_dim;
-    sm[i] = to_float(src[(size_t)h * qd + flat_dim + d]);
+  const T* src = q + ((size_t)t * n_heads + h0) * qd;
+  const int all_heads = n_heads;
+  n_heads = min(heads_per_block, n_heads - h0);  // from here on: the block's heads
+  // two values at a time where every offset is even (the rows themselves start on a multiple of their even widths)
+  const bool pairs = ((rot_dim | flat_dim | kv_rank | pad_dim) & 1) == 0;
+  if (pairs) {
+    const int half = rot_dim / 2;
+    for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
+      const int h = i / half, d = (i - h * half) * 2;
+      const float2 v = load2(src + (size_t)h * qd + flat_dim + d);
+      sm[h * rot_dim + d] = v.x;
+      sm[h * rot_dim + d + 1] = v.y;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n_heads * rot_dim; i += blockDim.x) {
+      const int h = i / rot_dim, d = i - h * rot_dim;
+      sm[i] = to_float(src[(size_t)h * qd + flat_dim + d]);
+    }
   }
   __syncthreads();
   int pos = positions[t];
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
   const float* tab = table ? table + (size_t)pos * n_rot : nullptr;
   const int tail = pad_dim - kv_rank;
-  T* dst = q_out + (size_t)t * n_heads * pad_dim;
+  T* dst = q_out + ((size_t)t * all_heads + h0) * pad_dim;
+  if (pairs) {
+    const int half = tail / 2;
+    for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
+      const int h = i / half, d = (i - h * half) * 2;
+      float2 v = make_float2(0.f, 0.f);
+      if (d < rot_dim) {
+        v.x = tab ? rotated_at(sm + h * rot_dim, d, n_rot, interleaved, tab) : sm[h * rot_dim + d];
+        v.y = tab ? rotated_at(sm + h * rot_dim, d + 1, n_rot, interleaved, tab) : sm[h * rot_dim + d + 1];
+      }
+      store2(dst + (size_t)h * pad_dim + kv_rank + d, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n_heads * tail; i += blockDim.x) {
     const int h = i / tail, d = i - h * tail;
     float v = 0.f;
@@ -137,16 +173,20 @@ extern "C" int ftk_latent_query_rotate(const void* q, int dtype, int n_heads, in
               pad_dim >= kv_rank + rot_dim && n_tokens >= 0, "latent_query_rotate: bad sizes");
   if (n_tokens == 0 || pad_dim == kv_rank) return 0;
   FTK_REQUIRE(q && positions && q_out && (n_rot == 0 || table), "latent_query_rotate: null pointer");
-  const size_t smem = (size_t)n_heads * rot_dim * sizeof(float) + 16;
-  FTK_REQUIRE(smem <= 48 * 1024, "latent_query_rotate: %d heads of %d rotated values do not fit", n_heads, rot_dim);
+  // a block takes a token's heads in groups that give its 128 threads two values each to read and pad_dim - kv_rank to write
+  const int per = max(1, min(n_heads, 256 / max(rot_dim, 1)));
+  const size_t smem = (size_t)per * rot_dim * sizeof(float) + 16;
+  FTK_REQUIRE(smem <= 48 * 1024, "latent_query_rotate: %d rotated values a head do not fit", rot_dim);
+  FTK_REQUIRE((n_heads + per - 1) / per <= 65535, "latent_query_rotate: too many heads");
+  const dim3 grid(n_tokens, (n_heads + per - 1) / per);
   cudaStream_t s = (cudaStream_t)stream;
   const float* tab = n_rot ? table : nullptr;
   if (dtype == FTK_F32)
-    FTK_LAUNCH(latent_query_rotate_kernel<float>, n_tokens, 128, smem, s, (const float*)q, n_heads, flat_dim, rot_dim, n_rot,
-               interleaved, positions, tab, max_pos, (float*)q_out, kv_rank, pad_dim);
+    FTK_LAUNCH(latent_query_rotate_kernel<float>, grid, 128, smem, s, (const float*)q, n_heads, flat_dim, rot_dim, n_rot,
+               interleaved, positions, tab, max_pos, (float*)q_out, kv_rank, pad_dim, per);
   else
-    FTK_LAUNCH(latent_query_rotate_kernel<__nv_bfloat16>, n_tokens, 128, smem, s, (const __nv_bfloat16*)q, n_heads, flat_dim,
-               rot_dim, n_rot, interleaved, positions, tab, max_pos, (__nv_bfloat16*)q_out, kv_rank, pad_dim);
+    FTK_LAUNCH(latent_query_rotate_kernel<__nv_bfloat16>, grid, 128, smem, s, (const __nv_bfloat16*)q, n_heads, flat_dim,
+               rot_dim, n_rot, interleaved, positions, tab, max_pos, (__nv_bfloat16*)q_out, kv_rank, pad_dim, per);
   FTK_LAUNCH_CHECK("latent_query_rotate");
   return 0;
 }

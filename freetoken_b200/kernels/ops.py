@@ -1231,9 +1231,9 @@ def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, c
                 state_slots: torch.Tensor, seg_info: torch.Tensor, n_segs: int, key_fac: torch.Tensor,
                 decay: torch.Tensor, m_out: torch.Tensor) -> None:
     """Gates of a matrix-memory layer for the step's tokens, per (request, head), all float32: with
-    ``i = cap tanh((pre_i + b_i) / cap)`` and ``f = logsigmoid(cap tanh((pre_f + b_f) / cap))``, ``key_fac = e^i``,
-    ``decay = e^f``, and the running maximum ``m_t = max(f_t + m_(t-1), i_t)``, which starts from
-    ``m_state[slot, head]`` (from 0 for a request's first tokens) and is left there.  ``pre [T, 2 H]``."""
+    ``i = cap tanh((pre_i + b_i) / cap)`` and ``f = logsigmoid(cap tanh((pre_f + b_f) / cap))``, the running maximum
+    ``m_t = max(f_t + m_(t-1), i_t)``, which starts from ``m_state[slot, head]`` (from 0 for a request's first tokens)
+    and is left there, ``key_fac = e^(i_t - m_t)`` and ``decay = e^(f_t + m_(t-1) - m_t)``.  ``pre [T, 2 H]``."""
     T, H2 = pre.shape
     H = H2 // 2
     if key_fac.shape != (T, H) or decay.shape != (T, H) or m_out.shape != (T, H) or m_state.shape[1:] != (H,):
@@ -1248,8 +1248,8 @@ def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, c
 
 def mlstm_output(o32: torch.Tensor, nq: torch.Tensor, m: torch.Tensor, gates: torch.Tensor, norm_weight: torch.Tensor,
                  eps: float, out: torch.Tensor) -> None:
-    """``o32 [T, H, vdim]`` (numerators), ``nq [T, H]`` (``n . q``), ``m [T, H]``: ``o = num / (max(|n . q|, 1) +
-    1e-6 e^m)``, divided by its root mean square over the head, times ``norm_weight [H * vdim]``, times
+    """``o32 [T, H, vdim]`` (numerators), ``nq [T, H]`` (``n . q``), ``m [T, H]``: ``o = num / (max(|n . q|, e^-m) +
+    1e-6)``, divided by its root mean square over the head, times ``norm_weight [H * vdim]``, times
     ``sigmoid(gates)`` (``gates [T, H * vdim]``, a view of adjacent columns is fine) into ``out [T, H * vdim]``."""
     T, H, Dv = o32.shape
     if out.shape != (T, H * Dv) or gates.shape != (T, H * Dv) or gates.stride(1) != 1 or gates.dtype != out.dtype \

@@ -10,12 +10,13 @@ gate ``i_t = cap tanh((W_i h_t + b_i) / cap)`` and a log forget gate ``f_t = log
 Each head's ``o_t`` is divided by its root mean square, multiplied by a weight (one per channel of all heads) and
 by ``sigmoid(W_g h_t)``, and projected.
 
-The state is kept as ``C_t = e^(m_t) S_t`` and ``N_t = e^(m_t) n_t`` (one tensor ``[H, D, Dv + 1]``: ``N`` is the
-recurrence of one more value column that is 1 for every token) and ``m_t``; then ``C_t = e^(f_t) C_(t-1) +
-(e^(i_t) k_t) v_t^T`` is the linear recurrence that :func:`ops.gla_scan` runs, chunked over long portions: it reads
-``q, k, v`` where the projection left them, multiplies a token's keys by ``e^(i_t)`` in 32 bits as it stages them,
-takes ``e^(f_t)`` as the head's one decay and adds the column of ones itself; and ``o_t = C_t^T q_t / (max(|N_t . q_t|, 1) + 1e-6 e^(m_t))``.  The capped gates keep ``C``
-far inside the 32-bit range.  Gates, state, the inputs of the recurrence and the output's norm are 32-bit;
+The state is ``S_t``, ``n_t`` (one tensor ``[H, D, Dv + 1]``: ``n`` is the recurrence of one more value column
+that is 1 for every token) and ``m_t``.  With ``m`` known, the recurrence is linear, with one decay ``e^(f_t + m_(t-1)
+- m_t)`` per head and token and keys times ``e^(i_t - m_t)`` (both at most 1, whatever the gates' cap):
+:func:`ops.mlstm_gates` scans ``m`` and writes both factors, and :func:`ops.gla_scan` runs the recurrence, chunked over
+long portions: it reads ``q, k, v`` where the projection left them, multiplies a token's keys by their factor in 32
+bits as it stages them and adds the column of ones itself.  Gates, state, the recurrence's sums and the output's norm
+are 32-bit;
 the projections are library products.  The state lives in a slot of the cache manager's state pool and starts
 from zero (and ``m`` from 0) for a request's first tokens.  The reference has no recurrent mixer.
 """
@@ -123,7 +124,7 @@ class MatrixMemory(Mixer):
             decay = ws.get("mlstm.decay", (n_chunks, H, D), f32, (most, H, D))
         o32 = ws.get("mlstm.o32", (T, H, Dv), f32, (cap, H, Dv))
         nq = ws.get("mlstm.nq", (T, H), f32, (cap, H))
-        # q, k, v where the projection left them; e^i on the keys, e^f as the head's decay, the normaliser's ones
+        # q, k, v where the projection left them; the key factor, the head's decay, the normaliser's ones
         ops.gla_scan(proj[:, : H * D], proj[:, H * D: 2 * H * D], proj[:, 2 * H * D: self.g_row], None, None, 1.0,
                      D ** -0.5, cache.tensors["s"], step.state_slots, step.seg_info, len(step.segments), tensors[name],
                      n_chunks, tensors[name + ".segments"], single, multi, carry, decay, o32, k_fac=kf, a_head=dec,

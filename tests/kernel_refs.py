@@ -524,20 +524,20 @@ def mlstm_gates(pre, bias_i, bias_f, cap, m_state, state_slots, seg_info, n_segs
     gi = cap * torch.tanh((pre[:, :H].float() + bias_i.float()) / cap)
     zf = cap * torch.tanh((pre[:, H:].float() + bias_f.float()) / cap)
     f = torch.nn.functional.logsigmoid(zf)
-    key_fac.copy_(torch.exp(gi))
-    decay.copy_(torch.exp(f))
     for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
         slot = int(state_slots[i])
         m = torch.zeros(H) if kv_len == q_len else m_state[slot].clone()
         for t in range(q_start, q_start + q_len):
-            m = torch.maximum(f[t] + m, gi[t])
-            m_out[t] = m
+            new = torch.maximum(f[t] + m, gi[t])
+            key_fac[t] = torch.exp(gi[t] - new)
+            decay[t] = torch.exp(f[t] + m - new)
+            m_out[t] = m = new
         m_state[slot] = m
 
 
 def mlstm_output(o32, nq, m, gates, norm_weight, eps, out):
     T, H, Dv = o32.shape
-    o = o32 / (torch.clamp(nq.abs(), min=1.0) + 1e-6 * torch.exp(m))[:, :, None]
+    o = o32 / (torch.maximum(nq.abs(), torch.exp(-m)) + 1e-6)[:, :, None]
     o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)
     y = o.reshape(T, H * Dv) * norm_weight.float() * torch.sigmoid(gates.float())
     out.copy_(y.to(out.dtype))

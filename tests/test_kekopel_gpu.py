@@ -304,7 +304,7 @@ def plain_memory(q, k, v, gi, f, m0, S0, n0):
 def test_matrix_memory_kernels_against_the_stated_recurrence(dtype, H, D, Dv, cap):
     """Gates, running maximum, the recurrence kernel on prepared inputs and the output step together, for requests that
     start and one that goes on from a state, portions longer than a chunk and single tokens; the state left behind
-    (C = e^m S, N = e^m n, m) is the stated one's."""
+    (S, n, m) is the stated one's."""
     lens = [(150, 150), (1, 20), (70, 90), (3, 3)]
     info, slots, T = segs(lens)
     proj = rnd(T, H * (2 * D + 2 * Dv), dtype=dtype, seed=1)
@@ -339,16 +339,14 @@ def test_matrix_memory_kernels_against_the_stated_recurrence(dtype, H, D, Dv, ca
         a, b = int(info[i, 0]), int(info[i, 0]) + q_len
         if kv_len == q_len:
             S, n, mm = torch.zeros(H, D, Dv).double(), torch.zeros(H, D).double(), torch.zeros(H).double()
-        else:  # the slot holds C = e^m S and N = e^m n
+        else:
             mm = m0[i + 1].cpu().double()
-            S = S0[i + 1, :, :, :Dv].cpu().double() * torch.exp(-mm)[:, None, None]
-            n = S0[i + 1, :, :, Dv].cpu().double() * torch.exp(-mm)[:, None]
+            S, n = S0[i + 1, :, :, :Dv].cpu().double(), S0[i + 1, :, :, Dv].cpu().double()
         o, S, n, mm = plain_memory(qq[a:b], kk[a:b], vv[a:b], g_i[a:b], g_f[a:b], mm, S, n)
         o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + 1e-5)
         want = o.reshape(q_len, H * Dv) * w.cpu().double() * torch.sigmoid(gates[a:b].float().cpu().double())
         torch.testing.assert_close(out[a:b].float().cpu().double(), want, **tol(dtype, f32=1e-4))
         torch.testing.assert_close(m_state[i + 1].cpu().double(), mm, rtol=1e-5, atol=1e-5)
-        S, n = S * torch.exp(mm)[:, None, None], n * torch.exp(mm)[:, None]
         for got_s, want_s in ((state[i + 1, :, :, :Dv], S), (state[i + 1, :, :, Dv], n)):  # (relative to the largest entry)
             torch.testing.assert_close(got_s.cpu().double() / want_s.abs().max(), want_s / want_s.abs().max(), rtol=1e-4, atol=1e-5)
 
