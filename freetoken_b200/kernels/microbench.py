@@ -359,7 +359,7 @@ def bench_kekopel(a) -> dict:
     bias = torch.randn(2 * H, device=dev, generator=g)
     m_state = torch.zeros(n_slots, H, device=dev)
     gi, zf, m = (torch.empty(T, H, device=dev) for _ in range(3))
-    add("mlstm_gates", lambda: ops.mlstm_gates(pre, bias[:H], bias[H:], 15.0, m_state, slots, seg, len(segs), gi, zf, m),
+    add("mlstm_gates", lambda: ops.mlstm_gates(pre, bias[:H], bias[H:], 12.0, m_state, slots, seg, len(segs), gi, zf, m),
         T * H * 4 * 5)
     wide = (torch.randn(T, H * (2 * D + 2 * Dv), device=dev, generator=g) * 0.3).to(bf)
     chunks, per_seg, single, multi = chunk_list(segs, a.chunk)

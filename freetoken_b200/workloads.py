@@ -172,8 +172,8 @@ def _design_configs(width, heads, kv, dim, experts, top, ff, vocab, layers):
     # (a cached row of 128 at the two smaller sizes, which the tcgen05 attention kernel takes, of 256 at the largest)
     rank, rot = (64, 64) if width <= 2048 else (192, 64)
     lat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "q_rank": width // 2, "kv_rank": rank,
-           "scale": (dim + rot) ** -0.5, "mask": {"size": window}, "rot": {"dims": rot, "base": 500000.0}}
-    mem = {"heads": heads, "dim": dim, "vdim": dim, "gate_cap": 15.0}
+           "scale": (dim + rot) ** -0.5, "mask": {"size": window}, "rot": {"dims": rot, "base": 1000000.0}}
+    mem = {"heads": heads, "dim": dim, "vdim": dim, "gate_cap": 12.0}
     kmlp = [{"kind": "dense", "ff": top * ff}, {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}]
     keko = {"architecture": "Kekopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
             "layers": [{"type": "mlstm" if i % 3 == 2 else "latent_attention", "mixer": dict(mem if i % 3 == 2 else lat),
