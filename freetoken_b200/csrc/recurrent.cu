@@ -132,7 +132,17 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
   for (int n = 0; n < NC; ++n)
 #pragma unroll
     for (int i = 0; i < DPT; ++i)
-      s[n][i] = (src && col + 32 * n < Dv && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + col + 32 * n] : 0.f;
+      s[n][i] = (src && col + 32 * n < Dvin && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + col + 32 * n] : 0.f;
+  // The column of ones (a normaliser: the decayed sum of the keys) is no value column of any thread: in the block of
+  // the first columns, lane l of a slice's warp keeps its key channels l, l + 32, ... of it, and the warp adds up n . q.
+  constexpr int NPL = (DPT + 31) / 32;
+  const bool norm_here = a.ones_col && blockIdx.z == 0 && group == 0;
+  float nn[NPL];
+#pragma unroll
+  for (int u = 0; u < NPL; ++u) {
+    const int i = lane + 32 * u;
+    nn[u] = (norm_here && src && i < DPT && d0 + i < D) ? src[(size_t)(d0 + i) * Dv + Dvin] : 0.f;
+  }
   float pa[MODE == 1 ? DPT : 1];  // MODE 1: the product of the chunk's decays (the lanes of a warp hold the same values)
   if (MODE == 1) {
 #pragma unroll
@@ -150,7 +160,8 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
   // from shared to shared memory widens them
   // (a chunk of one batch has nothing to fetch ahead of: it takes the direct way)
   const bool ahead = wide && ntok > kGlaBatch && Dvin % 8 == 0 && a.v_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15) == 0;
-  __nv_bfloat16* kraw = reinterpret_cast<__nv_bfloat16*>(part + kGlaSlices * kGlaBatch * cols);  // [batch][Dp]
+  float* npart = part + kGlaSlices * kGlaBatch * cols;  // [slices][batch]: the ones column's share of each slice
+  __nv_bfloat16* kraw = reinterpret_cast<__nv_bfloat16*>(npart + kGlaSlices * kGlaBatch);        // [batch][Dp]
   __nv_bfloat16* qraw = kraw + kGlaBatch * Dp;
   float* zraw = reinterpret_cast<float*>(qraw + kGlaBatch * Dp);                                  // [batch][Dp]
   __nv_bfloat16* vraw = reinterpret_cast<__nv_bfloat16*>(zraw + kGlaBatch * Dp);                  // [batch][cols]
@@ -228,7 +239,6 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
         const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vraw + i));
         sv[i] = f.x;
         sv[i + 1] = f.y;
-        if (a.ones_col && col0 + i % cols == Dvin) sv[i] = 1.f;  // Dvin is a multiple of 8 here, i is even
       }
       __syncthreads();
       if (b0 + kGlaBatch < ntok) fetch(b0 + kGlaBatch);  // the buffers are read: the next batch may land
@@ -293,8 +303,7 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
     for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
       const int t = i / cols, j = i % cols;
       const size_t tok = (size_t)(q_start + tok0 + b0 + t);
-      sv[i] = col0 + j < Dvin ? to_float(vb[tok * a.v_stride + (size_t)h * Dvin + col0 + j])
-                              : (a.ones_col && col0 + j == Dvin ? 1.f : 0.f);
+      sv[i] = col0 + j < Dvin ? to_float(vb[tok * a.v_stride + (size_t)h * Dvin + col0 + j]) : 0.f;
     }
     __syncthreads();
     }
@@ -335,20 +344,43 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
         for (int n = 0; n < NC; ++n)
           part[(slice * kGlaBatch + t) * cols + lcol + 32 * n] = (acc[n][0] + acc[n][1]) + (acc[n][2] + acc[n][3]);
       }
+      if (norm_here) {
+        float nq = 0.f;
+#pragma unroll
+        for (int u = 0; u < NPL; ++u) {
+          const int i = lane + 32 * u;
+          if (i < DPT) {
+            nn[u] = fmaf(sa[t * Dp + d0 + i], nn[u], sk[t * Dp + d0 + i]);
+            if (MODE != 1) nq = fmaf(nn[u], sq[t * Dp + d0 + i], nq);
+          }
+        }
+        if (MODE != 1) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) nq += __shfl_xor_sync(0xffffffffu, nq, o);
+          if (lane == 0) npart[slice * kGlaBatch + t] = nq;
+        }
+      }
     }
     if (MODE != 1) {
       __syncthreads();
       for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
         const int t = i / cols, j = i % cols;
-        if (col0 + j < Dv) {
+        if (col0 + j < Dvin) {
           float o = 0.f;
 #pragma unroll
           for (int w = 0; w < kGlaSlices; ++w) o += part[(w * kGlaBatch + t) * cols + j];  // slices in order
           const size_t row = (size_t)(q_start + tok0 + b0 + t) * a.H + h;
-          if (!a.out_ones) a.out[row * Dv + col0 + j] = o;
-          else if (col0 + j == Dvin) a.out_ones[row] = o;
-          else a.out[row * Dvin + col0 + j] = o;
+          a.out[row * (a.out_ones ? Dvin : Dv) + col0 + j] = o;
         }
+      }
+      if (norm_here && threadIdx.x < nb) {  // (group 0's threads: the first ones of the block)
+        const int t = threadIdx.x;
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kGlaSlices; ++w) o += npart[w * kGlaBatch + t];
+        const size_t row = (size_t)(q_start + tok0 + b0 + t) * a.H + h;
+        if (a.out_ones) a.out_ones[row] = o;
+        else a.out[row * Dv + Dvin] = o;
       }
     }
   }
@@ -361,7 +393,14 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
     for (int n = 0; n < NC; ++n)
 #pragma unroll
       for (int i = 0; i < DPT; ++i)
-        if (d0 + i < D && col + 32 * n < Dv) dst[(size_t)(d0 + i) * Dv + col + 32 * n] = s[n][i];
+        if (d0 + i < D && col + 32 * n < Dvin) dst[(size_t)(d0 + i) * Dv + col + 32 * n] = s[n][i];
+    if (norm_here) {
+#pragma unroll
+      for (int u = 0; u < NPL; ++u) {
+        const int i = lane + 32 * u;
+        if (i < DPT && d0 + i < D) dst[(size_t)(d0 + i) * Dv + Dvin] = nn[u];
+      }
+    }
   }
   if (MODE == 1 && blockIdx.z == 0 && group == 0 && lane == 0) {
 #pragma unroll
@@ -397,15 +436,16 @@ template <typename T, int DPT>
 static int launch_gla(GlaArgs a, bool any_single, bool any_multi, cudaStream_t s) {
   const int Dp = DPT * kGlaSlices;
   constexpr int kGlaCols = 32 * gla_cols_per_thread(DPT);
-  const int tiles = (a.Dv + kGlaCols - 1) / kGlaCols;
+  const int dv_real = a.Dv - a.ones_col;  // the column of ones rides in the block of the first columns
+  const int tiles = (dv_real + kGlaCols - 1) / kGlaCols;
   a.groups = min(tiles, gla_max_groups(DPT));
   const int cols = a.groups * kGlaCols;
   const int threads = a.groups * kGlaSlices * 32;
-  size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols) *
-                sizeof(float);
+  size_t smem = ((size_t)3 * kGlaBatch * Dp + (size_t)kGlaBatch * cols + (size_t)kGlaSlices * kGlaBatch * cols +
+                 (size_t)kGlaSlices * kGlaBatch) * sizeof(float);
   if (sizeof(T) == 2)  // the next batch as it lies in memory: q, k (bfloat16), decay logits (float), values (bfloat16)
     smem += (size_t)kGlaBatch * Dp * (2 + 2 + 4) + (size_t)kGlaBatch * cols * 2 + (size_t)2 * kGlaBatch * 4;
-  dim3 grid(a.n_chunks, a.H, (a.Dv + cols - 1) / cols);
+  dim3 grid(a.n_chunks, a.H, (dv_real + cols - 1) / cols);
   auto k0 = gla_chunk_kernel<T, DPT, 0>;
   auto k1 = gla_chunk_kernel<T, DPT, 1>;
   auto k3 = gla_chunk_kernel<T, DPT, 3>;
