@@ -55,7 +55,7 @@ class ParamSpec:
     32-bit path), ``"float32"`` (kept in 32-bit in both paths: norm scales, router
     matrices and biases) or ``"int32"`` (integer tables).
     ``init`` describes the random-weights distribution: ``("normal", mean, std)``,
-    ``("zeros",)`` or ``("ones",)``.  ``store`` is the dtype the random-weights writer
+    ``("uniform", low, high)``, ``("zeros",)`` or ``("ones",)``.  ``store`` is the dtype the random-weights writer
     uses in the file (``None``: bfloat16 for ``"compute"``, else ``dtype``).
     """
 

@@ -148,7 +148,11 @@ class Engine:
         self._views: List[Any] = []
         for i, e in enumerate(spec.schedule):
             owner = i if e.cache_from is None else e.cache_from
-            self._views.append(self.cache.view(owner))
+            n_branches = self.model.cache_branches(owner)
+            if n_branches:  # a mixer of several branches: a view per branch (None where a branch keeps nothing)
+                self._views.append(tuple(self.cache.view((owner, j)) for j in range(n_branches)))
+            else:
+                self._views.append(self.cache.view(owner))
         self._block_views: Dict[int, Any] = {i: self.cache.view(("block", i)) for i, _ in block_needs}
         self.buffers = StepBuffers(self.device, self._metadata_capacity())
         self.graphs: Dict[Any, Any] = {}
@@ -379,10 +383,12 @@ class Engine:
         return self.graph_logits[key]
 
     def _step_views(self, tensors: Dict[str, torch.Tensor]) -> List[Any]:
-        out = []
-        for v in self._views:
+        def of_step(v):
+            if isinstance(v, tuple):
+                return tuple(of_step(x) for x in v)
             if isinstance(v, PagedCacheView):
-                v = PagedCacheView(v.slabs, v.block_table, tensors[f"slot_map.{v.group.index}"],
-                                   v.page_size, v.window, v.group)
-            out.append(v)
-        return out
+                return PagedCacheView(v.slabs, v.block_table, tensors[f"slot_map.{v.group.index}"],
+                                      v.page_size, v.window, v.group)
+            return v
+
+        return [of_step(v) for v in self._views]

@@ -145,7 +145,14 @@ _SIGNATURES = {
     "ftk_mlstm_gates": [_vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp],
     "ftk_mlstm_output": [_vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "ftk_gla_scan": [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _i, _vp, _vp, _f, _f,
-                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
+                     _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp],
+    "ftk_hyper_step": [_vp, ctypes.c_longlong, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp],
+    "ftk_conv_act": [_vp, ctypes.c_longlong, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp],
+    "ftk_delta_scan": [_vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong, _vp, ctypes.c_longlong,
+                       _vp, ctypes.c_longlong, _i, _vp, _vp, _f, _f, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "ftk_ssm_gates": [_vp, ctypes.c_longlong, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "ftk_ssm_output": [_vp, _vp, ctypes.c_longlong, _vp, _vp, ctypes.c_longlong, _i, _vp, _i, _f, _vp, _i, _i, _i, _vp],
+    "ftk_norm_mean": [ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _i, _f, _vp, _i, _i, _vp],
 }
 _bound = False
 _launches = 0
@@ -1072,7 +1079,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
              n_segs: int, chunks: torch.Tensor, n_chunks: int, seg_chunks: torch.Tensor, any_single: bool,
              any_multi: bool, carry: Optional[torch.Tensor], decay_prod: Optional[torch.Tensor],
              out: torch.Tensor, k_fac: Optional[torch.Tensor] = None, a_head: Optional[torch.Tensor] = None,
-             ones_col: bool = False, out_ones: Optional[torch.Tensor] = None) -> None:
+             ones_col: bool = False, out_ones: Optional[torch.Tensor] = None, qk_div: int = 1) -> None:
     """Gated linear attention of the step's tokens, per (request, head):
     ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t q_scale)``, ``a_t = sigmoid(z_t + z_bias)^(1 / tau)``.
 
@@ -1087,10 +1094,17 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     float32 gives one decay per (token, head) for all key channels, and ``z`` is then ``None``; with ``ones_col``
     the state's last value column belongs to a value that is 1 for every token, and ``v`` is ``[T, H * (Dv - 1)]``
     (the sum of the keys under the same decays: a normaliser); with ``out_ones [T, H]`` that column's outputs go
-    there and ``out`` is ``[T, H, Dv - 1]``."""
+    there and ``out`` is ``[T, H, Dv - 1]``.
+
+    ``qk_div > 1``: queries and keys are shared by groups of that many heads (head ``h`` reads q/k head
+    ``h // qk_div``), and ``q, k`` are ``[T, (H / qk_div) * D]``; with ``a_head`` only."""
     T = out.shape[0]
     H, D, Dv = state.shape[1], state.shape[2], state.shape[3]
-    if q.shape != (T, H * D) or k.shape != (T, H * D) or v.shape != (T, H * (Dv - (1 if ones_col else 0))) \
+    qk_div = int(qk_div)
+    if qk_div < 1 or H % qk_div or (qk_div > 1 and a_head is None):
+        raise KernelError("gla_scan: qk_div must divide the heads and goes with a decay per head")
+    Hqk = H // qk_div
+    if q.shape != (T, Hqk * D) or k.shape != (T, Hqk * D) or v.shape != (T, H * (Dv - (1 if ones_col else 0))) \
             or out.shape != (T, H, Dv - (1 if out_ones is not None else 0)) or (z is None) == (a_head is None) or (z is not None and z.shape != (T, H * D)):
         raise KernelError("gla_scan: shapes do not agree")
     if out_ones is not None and not ones_col:
@@ -1117,7 +1131,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         _dev(carry, "carry", torch.float32), _dev(decay_prod, "decay_prod", torch.float32),
         _dev(out, "out", torch.float32), T, H, D, Dv, _dev(k_fac, "k_fac", torch.float32),
         _dev(a_head, "a_head", torch.float32), 1 if ones_col else 0, _dev(out_ones, "out_ones", torch.float32),
-        _stream()), "gla_scan", max(1, launches))
+        qk_div, _stream()), "gla_scan", max(1, launches))
 
 
 # --------------------------------------------------------------------------- short convolution, depth mix
@@ -1259,3 +1273,150 @@ def mlstm_output(o32: torch.Tensor, nq: torch.Tensor, m: torch.Tensor, gates: to
         _dev(o32, "o32", torch.float32), _dev(nq, "nq", torch.float32), _dev(m, "m", torch.float32), gates.data_ptr(),
         gates.stride(0) if T > 1 else H * Dv, _dev(norm_weight, "norm_weight", torch.float32), float(eps),
         _dev(out, "out"), _code(out, "out"), T, H, Dv, _stream()), "mlstm_output")
+
+
+# --------------------------------------------------------------------------- several residual streams
+def hyper_step(streams: torch.Tensor, init_from: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
+               mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None,
+               in_w: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+               h_out: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None) -> None:
+    """One pass over the ``S`` residual streams ``streams [S, T, C]`` (float32; a view whose streams lie
+    ``streams.stride(0)`` apart), every step optional, in this order:
+
+    * ``init_from [T, C]`` (float32): every stream becomes a copy of it;
+    * ``y [T, C]`` (a sub-layer's result), ``mix [S, S]`` indexed ``[from, to]``, ``out_w [S]``: all streams at once from
+      the old ones, ``x_t <- sum_s mix[s, t] x_s + out_w[t] y``;
+    * ``in_w [S]``, ``norm_w [C]``: ``h_out = unit(sum_s in_w[s] x_s) * norm_w`` with ``unit`` the division by the root
+      mean square (``eps`` inside the root); ``h_out [T, C]`` is float32 or of the engine's dtype;
+    * ``sum_out [T, C]`` (float32) ``= sum_s x_s``.
+
+    All sums are 32-bit; the streams are stored back when the first or second step changed them."""
+    S, T, C = streams.shape
+    if streams.dtype != torch.float32 or streams.stride(2) != 1 or streams.stride(1) != C or S > 8:
+        raise KernelError("hyper_step: streams must be float32 [S <= 8, T, C] with dense rows")
+    if (y is None) != (mix is None) or (y is None) != (out_w is None) or (in_w is None) != (norm_w is None) \
+            or (in_w is None) != (h_out is None):
+        raise KernelError("hyper_step: y goes with mix and out_w; in_w goes with norm_w and h_out")
+    for name, t, shape in (("init_from", init_from, (T, C)), ("y", y, (T, C)), ("mix", mix, (S, S)), ("out_w", out_w, (S,)),
+                           ("in_w", in_w, (S,)), ("norm_w", norm_w, (C,)), ("h_out", h_out, (T, C)),
+                           ("sum_out", sum_out, (T, C))):
+        if t is not None and tuple(t.shape) != shape:
+            raise KernelError(f"hyper_step: {name} must be {shape}, got {tuple(t.shape)}")
+    _check(_lib().ftk_hyper_step(
+        streams.data_ptr(), streams.stride(0), S, T, C, _dev(init_from, "init_from", torch.float32), _dev(y, "y"),
+        _code(y, "y") if y is not None else F32, _dev(mix, "mix", torch.float32), _dev(out_w, "out_w", torch.float32),
+        _dev(in_w, "in_w", torch.float32), _dev(norm_w, "norm_w", torch.float32), float(eps), _dev(h_out, "h_out"),
+        _code(h_out, "h_out") if h_out is not None else F32, _dev(sum_out, "sum_out", torch.float32), _stream()),
+        "hyper_step")
+
+
+def norm_mean(xs: Sequence[torch.Tensor], ws: Sequence[torch.Tensor], eps: float, out: torch.Tensor) -> None:
+    """``out = (1 / n) sum_i unit(xs[i]) * ws[i]``: up to four ``[T, C]`` tensors of ``out``'s dtype, each divided by
+    its rows' root mean square (``eps`` inside the root) and multiplied by a float32 weight ``[C]``; 32-bit sums."""
+    n = len(xs)
+    T, C = out.shape
+    if not 1 <= n <= 4 or len(ws) != n:
+        raise KernelError("norm_mean: one to four inputs, a weight each")
+    for x, w in zip(xs, ws):
+        if x.shape != (T, C) or x.dtype != out.dtype or w.shape != (C,):
+            raise KernelError("norm_mean: inputs [T, C] of out's dtype, weights [C]")
+    xp = (_vp * 4)(*[_dev(x, "x") for x in xs])
+    wp = (_vp * 4)(*[_dev(w, "w", torch.float32) for w in ws])
+    _check(_lib().ftk_norm_mean(xp, wp, n, _code(out, "out"), float(eps), _dev(out, "out"), T, C, _stream()), "norm_mean")
+
+
+CONV_ACT_CODES = {None: 0, "silu": 1}
+
+
+def conv_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], act: Optional[str],
+             state: Optional[torch.Tensor], state_slots: torch.Tensor, seg_info: torch.Tensor, n_segs: int,
+             out: torch.Tensor) -> None:
+    """``out[t] = act(bias + sum_j w[:, j] * in(t - taps + 1 + j))`` over each request's own inputs: a causal
+    convolution over time on every channel of a projection's rows.  ``x [T, C]`` of the engine's dtype (a view of
+    adjacent columns of a wider tensor is fine), ``w [C, taps]`` and ``bias [C]`` float32 (the last tap is the current
+    token's), ``act`` None or ``"silu"``, ``out [T, C]`` of ``x``'s dtype.  The request's last ``taps - 1`` inputs live
+    in ``state [slots, taps - 1, C]`` (float32, oldest first) at ``state_slots[segment]``: read for the step's first
+    tokens (zeros for a request whose first tokens these are) and replaced by the step's last inputs."""
+    T, C = x.shape
+    taps = w.shape[1]
+    if w.shape != (C, taps) or out.shape != (T, C) or out.dtype != x.dtype or x.stride(1) != 1 or not 1 <= taps <= 16:
+        raise KernelError("conv_act: x [T, C] with adjacent columns, w [C, taps <= 16], out [T, C] of x's dtype expected")
+    if taps > 1 and (state is None or state.shape[1:] != (taps - 1, C)):
+        raise KernelError("conv_act: state must be [slots, taps - 1, C]")
+    if bias is not None and bias.shape != (C,):
+        raise KernelError("conv_act: bias must be [C]")
+    if act not in CONV_ACT_CODES:
+        raise KernelError(f"conv_act: unknown activation '{act}'")
+    _check(_lib().ftk_conv_act(
+        x.data_ptr(), x.stride(0) if T > 1 else C, _code(x, "x"), _dev(w, "w", torch.float32),
+        _dev(bias, "bias", torch.float32), taps, CONV_ACT_CODES[act], _dev(state, "state", torch.float32),
+        state.shape[0] if state is not None else 0, _dev(state_slots, "state_slots", torch.int32),
+        _dev(seg_info, "seg_info", torch.int32), n_segs, _dev(out, "out"), T, C, _stream()), "conv_act")
+
+
+# --------------------------------------------------------------------------- state space, delta rule
+def _cols(t: torch.Tensor, what: str, shape, dtype: Optional[torch.dtype] = None) -> int:
+    """Row stride of a view of adjacent columns of a row-major tensor."""
+    if tuple(t.shape) != tuple(shape) or t.stride(1) != 1 or not t.is_cuda or (dtype is not None and t.dtype != dtype):
+        raise KernelError(f"{what} must be {tuple(shape)} with adjacent columns")
+    return t.stride(0) if t.shape[0] > 1 else t.shape[1]
+
+
+def ssm_gates(dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, dt_out: torch.Tensor,
+              decay_out: torch.Tensor) -> None:
+    """Step sizes and decays of a state-space layer, 32-bit: ``dt_out = softplus(dt_raw + dt_bias)`` (no clamp),
+    ``decay_out = exp(-exp(a_log) * dt_out)``; ``dt_raw [T, H]`` of the engine's dtype (a view of adjacent columns is
+    fine), ``dt_bias, a_log [H]`` and both outputs ``[T, H]`` float32."""
+    T, H = dt_out.shape
+    stride = _cols(dt_raw, "ssm_gates: dt_raw", (T, H))
+    if decay_out.shape != (T, H) or dt_bias.shape != (H,) or a_log.shape != (H,):
+        raise KernelError("ssm_gates: shapes do not agree")
+    _check(_lib().ftk_ssm_gates(dt_raw.data_ptr(), stride, _code(dt_raw, "dt_raw"), _dev(dt_bias, "dt_bias", torch.float32),
+                                _dev(a_log, "a_log", torch.float32), _dev(dt_out, "dt_out", torch.float32),
+                                _dev(decay_out, "decay_out", torch.float32), T, H, _stream()), "ssm_gates")
+
+
+def ssm_output(o32: torch.Tensor, x: torch.Tensor, d_skip: torch.Tensor, z: torch.Tensor, norm_weight: torch.Tensor,
+               norm_groups: int, eps: float, out: torch.Tensor) -> None:
+    """``y = (o32 + d_skip[head] * x) * silu(z)``, RMS-normed in ``norm_groups`` equal parts of a row (each by its own
+    root mean square, ``eps`` inside the root), times ``norm_weight [H * P]``, into ``out [T, H * P]``.  ``o32 [T, H, P]``
+    float32; ``x`` and ``z`` ``[T, H * P]`` of ``out``'s dtype (views of adjacent columns are fine); 32-bit arithmetic."""
+    T, H, P = o32.shape
+    xs = _cols(x, "ssm_output: x", (T, H * P), out.dtype)
+    zs = _cols(z, "ssm_output: z", (T, H * P), out.dtype)
+    if out.shape != (T, H * P) or d_skip.shape != (H,) or norm_weight.shape != (H * P,) or norm_groups < 1 \
+            or (H * P) % norm_groups:
+        raise KernelError("ssm_output: shapes do not agree")
+    _check(_lib().ftk_ssm_output(_dev(o32, "o32", torch.float32), x.data_ptr(), xs, _dev(d_skip, "d_skip", torch.float32),
+                                 z.data_ptr(), zs, _code(out, "out"), _dev(norm_weight, "norm_weight", torch.float32),
+                                 int(norm_groups), float(eps), _dev(out, "out"), T, H, P, _stream()), "ssm_output")
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_raw: torch.Tensor, a_raw: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, q_scale: float, unit_eps: float, state: torch.Tensor,
+               state_slots: torch.Tensor, seg_info: torch.Tensor, n_segs: int, out: torch.Tensor) -> None:
+    """The gated delta rule over the step's tokens, per (request, head), a request's tokens in order:
+    ``S <- g S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q``, with ``beta = sigmoid(b_raw)``,
+    ``g = exp(-exp(a_log) softplus(a_raw + dt_bias))``, and ``q``, ``k`` first made unit vectors per head
+    (``x / sqrt(sum(x^2) + unit_eps)``; ``q`` then times ``q_scale``).
+
+    ``q, k [T, G * D]``, ``v [T, H * Dv]``, ``b_raw, a_raw [T, H]`` of the engine's dtype (views of adjacent columns
+    are fine; head ``h`` reads q/k head ``h // (H / G)``); ``a_log, dt_bias [H]`` float32; ``state [slots, H, D, Dv]``
+    float32, read from and left in the slot ``state_slots[segment]`` (a segment with ``kv_len == q_len`` starts from
+    zero); ``out [T, H, Dv]`` float32.  Everything but the reading of the rows is 32-bit."""
+    T, H, Dv = out.shape
+    D = state.shape[2]
+    if state.shape[1] != H or state.shape[3] != Dv or q.shape[1] % D or H % (q.shape[1] // D) or D > 256:
+        raise KernelError("delta_scan: shapes do not agree (keys of at most 256 channels)")
+    G = q.shape[1] // D
+    qs, ks = _cols(q, "delta_scan: q", (T, G * D)), _cols(k, "delta_scan: k", (T, G * D), q.dtype)
+    vs = _cols(v, "delta_scan: v", (T, H * Dv), q.dtype)
+    bs, as_ = _cols(b_raw, "delta_scan: b_raw", (T, H), q.dtype), _cols(a_raw, "delta_scan: a_raw", (T, H), q.dtype)
+    if a_log.shape != (H,) or dt_bias.shape != (H,):
+        raise KernelError("delta_scan: a_log and dt_bias must be [H]")
+    _check(_lib().ftk_delta_scan(
+        q.data_ptr(), qs, k.data_ptr(), ks, v.data_ptr(), vs, b_raw.data_ptr(), bs, a_raw.data_ptr(), as_, _code(q, "q"),
+        _dev(a_log, "a_log", torch.float32), _dev(dt_bias, "dt_bias", torch.float32), float(q_scale), float(unit_eps),
+        _dev(state, "state", torch.float32), state.shape[0], _dev(state_slots, "state_slots", torch.int32),
+        _dev(seg_info, "seg_info", torch.int32), n_segs, _dev(out, "out", torch.float32), T, H, G, D, Dv, _stream()),
+        "delta_scan")

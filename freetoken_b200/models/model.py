@@ -89,14 +89,22 @@ class Model:
             self.head.tie(self.embedding)
 
     def cache_needs(self) -> List[Tuple[int, Any]]:
-        """(schedule entry, need) for every entry that owns a cache."""
+        """(schedule entry, need) for every entry that owns a cache.  A mixer of several branches states a tuple
+        of needs; each becomes ``((entry, branch), need)``."""
         out = []
         for i, e in enumerate(self.spec.schedule):
             if e.cache_from is None:
                 need = self.blocks[e.layer].mixer.cache_need()
-                if need is not None:
+                if isinstance(need, tuple):
+                    out += [((i, j), n) for j, n in enumerate(need) if n is not None]
+                elif need is not None:
                     out.append((i, need))
         return out
+
+    def cache_branches(self, entry: int) -> int:
+        """How many cache views the mixer of schedule entry ``entry`` takes (0: one view, not a tuple)."""
+        need = self.blocks[self.spec.schedule[entry].layer].mixer.cache_need()
+        return len(need) if isinstance(need, tuple) else 0
 
     def block_state_needs(self) -> List[Tuple[int, Any]]:
         """(schedule entry, need) for every entry whose block keeps a per-request state of its own."""

@@ -16,7 +16,10 @@ in the softmax's denominator (``sink``: a logit that takes its share of the weig
 output gate taken element by element from one more projection of the same input (``out_gate``), a layer
 without keys and values of its own that reads the cache of an earlier layer (``own_kv=False``; the
 schedule entry names the owner) and a cache that outlives the layer's own window because such readers
-look farther back (``cache_window``).
+look farther back (``cache_window``), biases on the q, k and v projections (``proj_bias``), one learned sink
+logit per head (``sink="learned"``), and a bias by the logarithm of the distance that is taken off the scaled score,
+``r1_h ln(1 + r2_h (i - j))`` with two learned numbers per head (``log_dist_bias``; the kernels read it from a table
+by distance that covers the engine's longest sequence, made in float64 and rounded once).
 """
 
 from __future__ import annotations
@@ -89,8 +92,8 @@ def attention_tile_rows(dtype: torch.dtype, decode_only: bool = False, group: in
 class GQAttention(Mixer):
     """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``qk_norm`` (bool),
     ``eps``, ``gemma`` (bool), ``position`` (PartSpec of a position encoding), ``window``
-    (None or tokens), ``scale`` (None = head_dim^-0.5); ``v_head_dim`` (head_dim), ``sink`` (None or a
-    logit), ``out_gate`` (None | "sigmoid" | "silu"), ``own_kv`` (True), ``cache_window`` (how long the
+    (None or tokens), ``scale`` (None = head_dim^-0.5); ``v_head_dim`` (head_dim), ``sink`` (None, a
+    logit, or "learned": a tensor of one logit per head), ``proj_bias`` (bool), ``log_dist_bias`` (bool), ``out_gate`` (None | "sigmoid" | "silu"), ``own_kv`` (True), ``cache_window`` (how long the
     cache keeps a token: ``window``, or more, or None for ever, when other layers read it), ``init_std``."""
 
     graph_safe = True  # running a step twice writes the same keys and values again
@@ -119,7 +122,11 @@ class GQAttention(Mixer):
             raise ConfigError("gqa_attention: a window holds at least the token itself")
         if self.cache_window is not None and (self.window is None or self.cache_window < self.window):
             raise ConfigError("gqa_attention: the cache must keep a token at least as long as the layer's window")
-        self.sink: Optional[float] = None if spec.get("sink") is None else float(spec["sink"])
+        self.learned_sink = spec.get("sink") == "learned"
+        self.sink: Optional[float] = None if spec.get("sink") is None or self.learned_sink else float(spec["sink"])
+        self.proj_bias = bool(spec.get("proj_bias", False))
+        self.log_dist_bias = bool(spec.get("log_dist_bias", False))
+        self._dist_table: Optional[torch.Tensor] = None
         self.out_gate: Optional[str] = spec.get("out_gate")
         if self.out_gate not in (None, "sigmoid", "silu"):
             raise ConfigError(f"gqa_attention: unknown output gate '{self.out_gate}'")
@@ -145,7 +152,8 @@ class GQAttention(Mixer):
         self.v_row = self.k_row + (self.kv_dim if self.own_kv else 0)
         self.g_row = self.v_row + (self.vv_dim if self.own_kv else 0)
         self.proj_rows = self.g_row + self.gate_dim
-        self.plain = not (self.padded or self.sink is not None or self.out_gate or self.kv_split > 1 or not self.own_kv)
+        self.plain = not (self.padded or self.sink is not None or self.out_gate or self.kv_split > 1 or not self.own_kv
+                          or self.learned_sink or self.proj_bias or self.log_dist_bias)
         self._o_weight: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ tensors
@@ -163,7 +171,29 @@ class GQAttention(Mixer):
             out["q_norm.weight"] = ParamSpec((self.head_dim,), "float32", init, store="bfloat16")
             if self.own_kv:
                 out["k_norm.weight"] = ParamSpec((self.head_dim,), "float32", init, store="bfloat16")
+        f32 = dict(dtype="float32", store="bfloat16")
+        if self.proj_bias:
+            out["q_bias"] = ParamSpec((self.q_dim,), init=("normal", 0.0, 0.3 if std else 0.02), **f32)
+            if self.own_kv:
+                out["k_bias"] = ParamSpec((self.kv_dim,), init=("normal", 0.0, 0.3 if std else 0.02), **f32)
+                out["v_bias"] = ParamSpec((self.vv_dim,), init=("normal", 0.0, 0.3 if std else 0.02), **f32)
+        if self.learned_sink:
+            out["sink"] = ParamSpec((self.n_heads,), init=("normal", 0.0, 1.0 if std else 0.02), **f32)
+        if self.log_dist_bias:
+            out["r1"] = ParamSpec((self.n_heads,), init=("normal", 0.5 if std else 0.0, 0.2 if std else 0.02), **f32)
+            out["r2"] = ParamSpec((self.n_heads,), init=("uniform", 0.05, 1.0), **f32)
         return out
+
+    def dist_table(self) -> Optional[torch.Tensor]:
+        """``[heads, longest sequence]``: what distance ``d`` adds to a head's scaled scores, ``-r1 ln(1 + r2 d)``;
+        made at the first call, when the engine's longest sequence is settled."""
+        if not self.log_dist_bias:
+            return None
+        if self._dist_table is None:
+            r1, r2 = self.params["r1"].double()[:, None], self.params["r2"].double()[:, None]
+            d = torch.arange(max(1, int(self.env.max_seq_len)), dtype=torch.float64, device=r1.device)[None, :]
+            self._dist_table = (-r1 * torch.log1p(r2 * d)).float().contiguous()
+        return self._dist_table
 
     def bind(self, tensors) -> None:
         super().bind(tensors)
@@ -173,6 +203,7 @@ class GQAttention(Mixer):
             wp[:, :, : self.v_dim] = w.view(self.hidden, self.n_heads, self.v_dim)
             w = wp.view(self.hidden, self.n_heads * self.pad_dim)
         self._o_weight = w
+        self._dist_table = None
 
     def cache_need(self):
         if not self.own_kv:
@@ -191,10 +222,13 @@ class GQAttention(Mixer):
     def kernel_form(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0):
         # (the tcgen05 kernels take no split KV heads; a sink or a window goes with the 128-row form alone)
         sized = self.kv_split == 1
-        special = self.sink is not None or self.window is not None
+        has_sink = self.sink is not None or self.learned_sink
+        if has_sink and self.log_dist_bias:  # (a sink together with a bias by distance: the tiles of 16 / 64 rows take both)
+            sized = False
+        special = has_sink or self.window is not None
         return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens,
                                      self.pad_dim if sized else 0, page_size, self.window, longest_span,
-                                     one_tile_only=special, no_few=special)
+                                     one_tile_only=special or self.log_dist_bias, no_few=special)
 
     def tile_rows(self, decode_only: bool, n_tokens: int = 0, page_size: int = 0, longest_span: int = 0) -> int:
         return self.kernel_form(decode_only, n_tokens, page_size, longest_span)[0]
@@ -210,7 +244,8 @@ class GQAttention(Mixer):
         # forward() of the same step runs the kernel this work list was made for
         rows, few_rows = self.kernel_form(builder.decode_only, n_tokens, page_size, builder.longest_span())
         if rows >= 128 and not few_rows and not builder.decode_only and n_tokens >= TC_PAIR_MIN_TOKENS_LONG \
-                and self.sink is None and self.window is None and hasattr(builder, "cheaper_attention_rows"):
+                and self.sink is None and not self.learned_sink and not self.log_dist_bias and self.window is None \
+                and hasattr(builder, "cheaper_attention_rows"):
             # one or two query tiles a piece: whichever work list the kernel is estimated to get through sooner
             rows = builder.cheaper_attention_rows(self.plan_group, self.window, self.plan_kv_heads, self.pad_dim)
         self._step_plan = builder.attention_plan(self.plan_group, rows, self.window, self.plan_kv_heads, self.pad_dim,
@@ -259,14 +294,16 @@ class GQAttention(Mixer):
         ops.linear(h, self.params["qkv_proj.weight"], proj)
         q = ws.get("attn.q", (T, H, Dp), dt, (cap, H, Dp))
         sections = [dict(first_head=0, n_heads=H, norm_weight=self.params.get("q_norm.weight"), rotate=True,
-                         dense_out=q, dst_head_dim=Dp)]
+                         dense_out=q, dst_head_dim=Dp, bias=self.params.get("q_bias"))]
         v_too = self.own_kv and Dv == D  # the value heads then lie on the same grid of heads as q and k
         if self.own_kv:
             sections.append(dict(first_head=H, n_heads=G, norm_weight=self.params.get("k_norm.weight"), rotate=True,
-                                 slab=cache.slabs["k"], slot_map=cache.slot_map, dst_head_dim=Dp))
+                                 slab=cache.slabs["k"], slot_map=cache.slot_map, dst_head_dim=Dp,
+                                 bias=self.params.get("k_bias")))
             if v_too:
                 sections.append(dict(first_head=H + G, n_heads=G, norm_weight=None, rotate=False,
-                                     slab=cache.slabs["v"], slot_map=cache.slot_map, dst_head_dim=Dp))
+                                     slab=cache.slabs["v"], slot_map=cache.slot_map, dst_head_dim=Dp,
+                                     bias=self.params.get("v_bias")))
         ops.norm_rope_store(proj, D, self.rotary_dim, step.positions, self.position.table(), self.eps, self.gemma,
                             sections)
         if self.own_kv and not v_too:  # values of another size: a pass of their own over a copy of their columns
@@ -274,13 +311,14 @@ class GQAttention(Mixer):
             v.copy_(proj[:, self.v_row: self.g_row])
             ops.norm_rope_store(v, Dv, 0, step.positions, None, self.eps, self.gemma,
                                 [dict(first_head=0, n_heads=G, norm_weight=None, rotate=False, slab=cache.slabs["v"],
-                                      slot_map=cache.slot_map, dst_head_dim=Dp)])
+                                      slot_map=cache.slot_map, dst_head_dim=Dp, bias=self.params.get("v_bias"))])
         plan = step.attention_plans[self._step_plan]
         o = ws.get("attn.o", (T, H, Dp), dt, (cap, H, Dp))
         ops.paged_attention(q, cache.slabs["k"], cache.slabs["v"], cache.block_table, step.seg_info,
                             len(step.segments), plan.items_dev, plan.n_items, plan.part_o, plan.part_ml,
                             o, self._step_plan[2], self.scale, self.window, few_rows=self._step_plan[6],
-                            kv_split=self.kv_split, sink=self.sink)
+                            kv_split=self.kv_split, sink=self.params["sink"] if self.learned_sink else self.sink,
+                            dist_bias=self.dist_table())
         if self.out_gate:
             ops.gated_heads(o, proj[:, self.g_row:], o, Dv, self.out_gate)
         out = ws.get("attn.out", (T, self.hidden), dt, (cap, self.hidden))

@@ -292,10 +292,31 @@ class NormedSum:
         ops.postnorm_add_norm(rows, routed, self.norm.params["weight"], self.norm.eps, self.norm.gemma, residual)
 
 
+class HyperSum:
+    """A sub-layer output that is still to be written into a layer stack's several residual streams
+    (hyper-connections): ``x_t <- sum_s mix[s, t] x_s + out[t] y`` for the streams ``streams [S, T, hidden]``
+    (32-bit).  A ``hyper_residual`` block takes it in the pass that reads the streams for its own first sub-layer;
+    for any other consumer :meth:`fold` writes it and leaves the sum of the streams in the one-stream residual."""
+
+    def __init__(self, y: torch.Tensor, streams: torch.Tensor, mix: torch.Tensor, out: torch.Tensor):
+        self.y, self.streams, self.mix, self.out = y, streams, mix, out
+
+    def fold(self, residual: torch.Tensor) -> None:
+        from ..kernels import ops
+
+        ops.hyper_step(self.streams, y=self.y, mix=self.mix, out_w=self.out, sum_out=residual)
+
+
 def as_rows(x: Any, consumer: Any = None, residual: Optional[torch.Tensor] = None) -> Any:
     """``x`` as the consumer can take it: a :class:`RouteSum` stays one only for a norm that says it
     takes one; a :class:`StreamSum` stays one only for a norm with ``takes_stream_sum`` and is otherwise
-    added to ``residual`` at once (nothing is then left to hand on)."""
+    added to ``residual`` at once (nothing is then left to hand on); a :class:`HyperSum` is written to its
+    streams, whose sum then is the residual."""
+    if isinstance(x, HyperSum):
+        if residual is None:
+            raise ConfigError("a HyperSum needs the stream that takes the sum of its streams")
+        x.fold(residual)
+        return None
     if isinstance(x, NormedSum) and not getattr(consumer, "takes_normed_sum", False):
         if residual is None:
             raise ConfigError("a NormedSum needs the stream to be added to")

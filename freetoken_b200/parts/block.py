@@ -20,6 +20,14 @@ and are normed on their way out only, ``r += ls1 * g1 * unit(mixer(r + conv1(r))
 ``ls`` a vector: together one weight vector of an RMS norm).  With ``depth_mix`` the layer then hands on a learned
 mix of the outputs of all layers so far (and the embedding): ``r <- sum_(j <= depth + 1) mix[j] X_j``.  The
 convolutions' last inputs are per-request state of the block (:meth:`Block.state_need`).
+
+``hyper_residual``: the residual is carried in ``streams`` copies (hyper-connections), all equal to the embedding at
+the start.  Sub-layer ``q`` reads ``u = sum_s in_q[s] x_s``, runs on ``N_q(u)``, and its result ``y`` goes back into
+every stream while the streams are mixed, ``x_t <- sum_s mix_q[s, t] x_s + out_q[t] y``; after the last layer the
+stream is the sum of the copies.  Without ``streams`` the same code runs one copy with all coefficients 1, which
+is the plain pre-norm residual.  With ``token_shift`` the mixer's input is first blended, channel by channel, with
+the input it had at the token before: ``h_t + (h_(t-1) - h_t) * shift`` (zeros before a sequence's start); the last
+input is per-request state of the block.
 """
 
 from __future__ import annotations
@@ -31,7 +39,7 @@ import torch
 from ..config.spec import ParamSpec, PartSpec, StateNeed
 from ..errors import ConfigError
 from ..kernels import ops
-from .base import (BLOCKS, FEED_FORWARDS, NORMS, Block, BuildEnv, FeedForward, Mixer, NormedSum, Part, RouteSum, StepState,
+from .base import (BLOCKS, FEED_FORWARDS, NORMS, Block, BuildEnv, FeedForward, HyperSum, Mixer, NormedSum, Part, RouteSum, StepState,
                    StreamSum, as_rows, nvtx_range)
 
 
@@ -270,3 +278,126 @@ class ConvPostNormResidualBlock(Block):
         if self.mixes:
             ops.depth_mix(hist, self.depth + 1, self.params["dwa"], residual[:T])
         return None
+
+
+@BLOCKS.register("hyper_residual")
+class HyperResidualBlock(Block):
+    """params: ``hidden``, ``streams`` (None or 0: one stream, no coefficients in the file), ``eps`` (of the two RMS
+    norms, plain weights), ``token_shift`` (bool), ``last`` (the stack's last layer leaves the streams' sum in the one stream; a layer
+    that is handed no pending write of its own streams copies the one stream into every stream first), ``init_std``.
+
+    Tensors: ``norm1``, ``norm2`` ``[hidden]``; with streams ``hc1.in``, ``hc1.out`` ``[S]``, ``hc1.mix`` ``[S, S]``
+    (indexed ``[from, to]``) and the same under ``hc2``; ``shift [hidden]``.  A layer without feed-forward has none
+    of the second ones."""
+
+    graph_safe = False  # the shift's state moves on with every run of a step
+    graph_recordable = True
+
+    def __init__(self, spec: PartSpec, env: BuildEnv, mixer: Mixer, ffn: FeedForward,
+                 mixer_name: str, ffn_name: str):
+        super().__init__(spec, env, mixer, ffn, mixer_name, ffn_name)
+        self.hidden = int(spec["hidden"])
+        self.file_streams = int(spec.get("streams") or 0)
+        self.streams = max(1, self.file_streams)
+        if self.streams > 8:
+            raise ConfigError(f"hyper_residual: {self.streams} streams (at most 8 taken)")
+        self.eps = float(spec["eps"])
+        self.shifts = bool(spec.get("token_shift", False))
+        self.last = bool(spec.get("last", False))
+        self.has_ffn = not isinstance(ffn, NoFeedForward)
+        if not self.shifts:
+            self.graph_safe = True
+        self._ones = None
+        self._shift_w = None
+
+    def children(self) -> Dict[str, Part]:
+        out = {self.mixer_name: self.mixer}
+        if self.has_ffn:
+            out[self.ffn_name] = self.ffn
+        return out
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        wide = self.spec.get("init_std") is not None
+        f32 = dict(dtype="float32", store="bfloat16")
+        S = self.file_streams
+        out: Dict[str, ParamSpec] = {}
+        for n in ("1", "2") if self.has_ffn else ("1",):
+            out["norm" + n] = ParamSpec((self.hidden,), init=("normal", 1.0, 0.2 if wide else 0.02), **f32)
+            if S:
+                out[f"hc{n}.in"] = ParamSpec((S,), init=("normal", 1.0 / S, 0.3 / S if wide else 0.02), **f32)
+                out[f"hc{n}.out"] = ParamSpec((S,), init=("normal", 1.0, 0.3 if wide else 0.02), **f32)
+                out[f"hc{n}.mix"] = ParamSpec((S, S), init=("normal", 1.0 / S, 0.5 / S if wide else 0.02), **f32)
+        if self.shifts:
+            out["shift"] = ParamSpec((self.hidden,), init=("normal", 0.5 if wide else 0.0, 0.2 if wide else 0.02), **f32)
+        return out
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if not self.file_streams:
+            dev = self.params["norm1"].device
+            self._ones = torch.ones((1, 1), dtype=torch.float32, device=dev)
+        if self.shifts:  # h + (h' - h) * shift as a two-tap convolution added to the input: taps (shift, -shift)
+            mu = self.params["shift"]
+            self._shift_w = torch.stack([mu, -mu], dim=1).contiguous()
+
+    def _hc(self, n: str):
+        """(in [S], out [S], mix [S, S]) of sub-layer ``n``."""
+        if not self.file_streams:
+            return self._ones.view(1), self._ones.view(1), self._ones
+        return self.params[f"hc{n}.in"], self.params[f"hc{n}.out"], self.params[f"hc{n}.mix"]
+
+    def state_need(self):
+        """The block's own per-request state: the mixer's last input before the shift, 32-bit."""
+        if not self.shifts:
+            return None
+        return StateNeed((("shift", (1, self.hidden), "float32"),))
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        item = 4 if self.env.dtype == torch.float32 else 2
+        return n_tokens * self.hidden * (self.streams * 4 + 4 + 2 * item)
+
+    def forward(self, x, residual: torch.Tensor, step: StepState, cache: Any, writes_cache: bool):
+        T = residual.shape[0]
+        ws, dt, cap = self.env.workspace, self.env.dtype, self.env.max_step_tokens
+        S = self.streams
+        streams = ws.get("block.streams", (S, cap, self.hidden), torch.float32)[:, :T]
+        pending = None
+        if isinstance(x, HyperSum) and x.streams.data_ptr() == streams.data_ptr() and x.streams.shape == streams.shape:
+            pending = x  # the layer before left its last write to be done with this layer's first read
+        elif x is not None:
+            x = as_rows(x, None, residual)
+            if x is not None:
+                StreamSum.of(x).fold(residual)
+        init = residual if pending is None else None  # the streams start as copies of the one stream
+        in1, out1, mix1 = self._hc("1")
+        h = ws.get("block.h", (T, self.hidden), dt, (cap, self.hidden))
+        if self.shifts:
+            state = step.block_states.get(step.entry)
+            if state is None:
+                raise ConfigError("hyper_residual: the engine gave the block no state for the token shift")
+            h32 = ws.get("block.h_f32", (T, self.hidden), torch.float32, (cap, self.hidden))
+            first_out = h32
+        else:
+            first_out = h
+        ops.hyper_step(streams, init_from=init, y=pending.y if pending else None, mix=pending.mix if pending else None,
+                       out_w=pending.out if pending else None, in_w=in1, norm_w=self.params["norm1"], eps=self.eps,
+                       h_out=first_out)
+        if self.shifts:
+            ops.short_conv(h32, self._shift_w, state.tensors["shift"], step.state_slots, step.seg_info,
+                           len(step.segments), h)
+        with nvtx_range(f"mixer {self.mixer.kind}"):
+            a = as_rows(self.mixer.forward(h, step, cache, writes_cache))
+        if not self.has_ffn:
+            if self.last:
+                ops.hyper_step(streams, y=a, mix=mix1, out_w=out1, sum_out=residual)
+                return None
+            return HyperSum(a, streams, mix1, out1)
+        in2, out2, mix2 = self._hc("2")
+        h2 = ws.get("block.h2", (T, self.hidden), dt, (cap, self.hidden))
+        ops.hyper_step(streams, y=a, mix=mix1, out_w=out1, in_w=in2, norm_w=self.params["norm2"], eps=self.eps, h_out=h2)
+        with nvtx_range(f"feed-forward {self.ffn.kind}"):
+            f = as_rows(self.ffn.forward(h2, step))
+        if self.last:
+            ops.hyper_step(streams, y=f, mix=mix2, out_w=out2, sum_out=residual)
+            return None
+        return HyperSum(f, streams, mix2, out2)

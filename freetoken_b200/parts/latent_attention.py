@@ -16,6 +16,10 @@ latent space (a product per head) and attention runs as one KV head of size ``kv
 (:func:`ops.paged_attention` with one slab for keys and values); sliding window, a learned sink per head in the
 softmax's denominator and the scale are their options.  Norms, rotation and softmax are 32-bit.
 
+Without a query latent (``q_rank = None``) the queries are a plain projection of the input, ``q_h = W_q,h h``.  With
+``head_gate`` every head's output is multiplied by ``sigmoid(w_g,h . h)``, one logit per head from one more row of
+the input projection.
+
 ``kv_rank + rot_dim`` may be at most 256 (the attention kernels' largest head); the tcgen05 kernels take it
 when it is 128.  The reference has no such layer.
 """
@@ -38,7 +42,7 @@ from .rope import shared_position
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     """params: ``hidden``, ``n_heads``, ``head_dim`` (unrotated), ``rot_dim`` (rotated, one key part for all heads),
-    ``v_head_dim``, ``q_rank``, ``kv_rank``, ``eps`` (of the latents' norms), ``position`` (PartSpec of a rotary
+    ``v_head_dim``, ``q_rank`` (None: no query latent), ``kv_rank``, ``head_gate`` (bool), ``eps`` (of the latents' norms), ``position`` (PartSpec of a rotary
     encoding whose ``rotary_dim <= rot_dim``), ``window`` (None or tokens), ``scale`` (None = (head_dim +
     rot_dim)^-0.5), ``sink`` (None | "learned": one logit per head), ``init_std``."""
 
@@ -48,8 +52,12 @@ class LatentAttention(Mixer):
         super().__init__(spec, env)
         g = lambda k: int(spec[k])  # noqa: E731
         self.hidden, self.n_heads, self.head_dim, self.rot_dim = g("hidden"), g("n_heads"), g("head_dim"), g("rot_dim")
-        self.v_dim, self.q_rank, self.kv_rank = g("v_head_dim"), g("q_rank"), g("kv_rank")
-        if min(self.hidden, self.n_heads, self.head_dim, self.v_dim, self.q_rank, self.kv_rank) < 1 or self.rot_dim < 0:
+        self.v_dim, self.kv_rank = g("v_head_dim"), g("kv_rank")
+        self.q_latent = spec.get("q_rank") is not None
+        self.q_rank = g("q_rank") if self.q_latent else 0
+        self.head_gate = bool(spec.get("head_gate", False))
+        if min(self.hidden, self.n_heads, self.head_dim, self.v_dim, self.kv_rank) < 1 or self.rot_dim < 0 \
+                or (self.q_latent and self.q_rank < 1):
             raise ConfigError("latent_attention: sizes must be positive")
         self.key_dim = self.kv_rank + self.rot_dim
         if self.key_dim > 256:
@@ -70,7 +78,9 @@ class LatentAttention(Mixer):
         if self.n_rot > self.rot_dim:
             raise ConfigError("latent_attention: more rotated dimensions than the rotated part has")
         self.q_dim = self.head_dim + self.rot_dim
-        self.in_rows = self.q_rank + self.kv_rank + self.rot_dim
+        # rows of the input projection: [query latent |] key/value latent | rotated key part [| a gate logit per head]
+        self.lat_rows = self.q_rank + self.kv_rank + self.rot_dim
+        self.in_rows = self.lat_rows + (self.n_heads if self.head_gate else 0)
         most = 16 if env.dtype != torch.bfloat16 else 64  # query heads on the one KV head that a tile's rows take
         self.kv_split = next(s for s in range(1, self.n_heads + 1) if self.n_heads % s == 0 and self.n_heads // s <= most)
         self.plan_group = self.n_heads // self.kv_split
@@ -84,13 +94,15 @@ class LatentAttention(Mixer):
         H = self.n_heads
         out = {
             "in_proj.weight": ParamSpec((self.in_rows, self.hidden), init=("normal", 0.0, s_in)),
-            "q_norm.weight": ParamSpec((self.q_rank,), "float32", ("normal", 1.0, 0.2 if std else 0.02), store="bfloat16"),
             "kv_norm.weight": ParamSpec((self.kv_rank,), "float32", ("normal", 1.0, 0.2 if std else 0.02), store="bfloat16"),
-            "q_up.weight": ParamSpec((H * self.q_dim, self.q_rank), init=("normal", 0.0, s_q)),
+            "q_up.weight": ParamSpec((H * self.q_dim, self.q_rank if self.q_latent else self.hidden),
+                                     init=("normal", 0.0, s_q if self.q_latent else s_in)),
             "k_up.weight": ParamSpec((H * self.head_dim, self.kv_rank), init=("normal", 0.0, s_kv)),
             "v_up.weight": ParamSpec((H * self.v_dim, self.kv_rank), init=("normal", 0.0, s_kv)),
             "o_proj.weight": ParamSpec((self.hidden, H * self.v_dim), init=("normal", 0.0, s_out)),
         }
+        if self.q_latent:
+            out["q_norm.weight"] = ParamSpec((self.q_rank,), "float32", ("normal", 1.0, 0.2 if std else 0.02), store="bfloat16")
         if self.sink == "learned":
             out["sink"] = ParamSpec((H,), "float32", ("normal", 0.0, 1.0 if std else 0.02), store="bfloat16")
         return out
@@ -140,10 +152,11 @@ class LatentAttention(Mixer):
         cq = ws.get("latent.cq", (T, self.q_rank), dt, (cap, self.q_rank))
         slab = cache.slabs["kv"]
         table = self.position.table()
-        ops.latent_store(proj, self.q_rank, C, R, self.n_rot, self.interleaved, self.params["q_norm.weight"],
-                         self.params["kv_norm.weight"], self.eps, step.positions, table, cq, slab, cache.slot_map)
+        ops.latent_store(proj[:, : self.lat_rows], self.q_rank, C, R, self.n_rot, self.interleaved,
+                         self.params.get("q_norm.weight"), self.params["kv_norm.weight"], self.eps, step.positions, table,
+                         cq, slab, cache.slot_map)
         q = ws.get("latent.q", (T, H, self.q_dim), dt, (cap, H, self.q_dim))
-        ops.linear(cq, self.params["q_up.weight"], q.view(T, H * self.q_dim))
+        ops.linear(cq if self.q_latent else h, self.params["q_up.weight"], q.view(T, H * self.q_dim))
         qa = ws.get("latent.q_abs", (T, H, P), dt, (cap, H, P))
         ops.heads_linear(q[:, :, :D], self._w_uk, qa[:, :, :C])
         ops.latent_query_rotate(q, D, R, self.n_rot, self.interleaved, step.positions, table, qa, C)
@@ -154,6 +167,8 @@ class LatentAttention(Mixer):
                             few_rows=self._step_plan[6], kv_split=self.kv_split, sink=self.params.get("sink"))
         ov = ws.get("latent.ov", (T, H, Dv), dt, (cap, H, Dv))
         ops.heads_linear(o[:, :, :C], self._w_uv, ov)
+        if self.head_gate:
+            ops.head_gate(ov, proj[:, self.lat_rows:])
         out = ws.get("latent.out", (T, self.hidden), dt, (cap, self.hidden))
         ops.linear(ov.view(T, H * Dv), self.params["o_proj.weight"], out)
         return out

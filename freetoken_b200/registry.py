@@ -39,6 +39,7 @@ _LAZY: Dict[str, str] = {
     "Rumalorn": "freetoken_b200.models.rumalorn",
     "Pabavik": "freetoken_b200.models.pabavik",
     "Kekopel": "freetoken_b200.models.kekopel",
+    "Nusudra": "freetoken_b200.models.nusudra",
 }
 
 

@@ -48,6 +48,11 @@ def _draw(ps: ParamSpec, gen: torch.Generator, device, dtype: torch.dtype) -> to
         t = torch.empty(ps.shape, dtype=torch.float32 if dtype != torch.bfloat16 else dtype, device=device)
         t.normal_(mean, std, generator=gen)
         return t.to(dtype)
+    if kind == "uniform":  # ("uniform", low, high)
+        _, low, high = ps.init
+        t = torch.empty(ps.shape, dtype=torch.float32, device=device)
+        t.uniform_(low, high, generator=gen)
+        return t.to(dtype)
     if kind == "distinct_ids":  # rows of different ids below ps.init[1] (a table that names experts)
         n = int(ps.init[1])
         rows, k = ps.shape

@@ -414,9 +414,13 @@ def gated_heads(x, gates, out, dim, act="sigmoid", norm_weight=None, eps=0.0):
 
 
 def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, seg_info, n_segs, chunks, n_chunks, seg_chunks,
-             any_single, any_multi, carry, decay_prod, out, k_fac=None, a_head=None, ones_col=False, out_ones=None):
+             any_single, any_multi, carry, decay_prod, out, k_fac=None, a_head=None, ones_col=False, out_ones=None,
+             qk_div=1):
     """Token by token from each request's slot; the chunk lists only steer how the kernel shares the work."""
     H, D, Dv = state.shape[1:]
+    if qk_div > 1:  # queries and keys shared by groups of heads
+        q = q.float().view(-1, H // qk_div, D).repeat_interleave(qk_div, dim=1).reshape(-1, H * D)
+        k = k.float().view(-1, H // qk_div, D).repeat_interleave(qk_div, dim=1).reshape(-1, H * D)
     if a_head is not None:
         decay = a_head.float()[:, :, None].expand(-1, H, D)
     else:
@@ -499,7 +503,8 @@ def latent_store(proj, q_rank, kv_rank, rot_dim, n_rot, interleaved, wq, wkv, ep
                  slot_map):
     p = proj.float()
     a, c, kr = p[:, :q_rank], p[:, q_rank:q_rank + kv_rank], p[:, q_rank + kv_rank:]
-    cq_out.copy_((a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps) * wq.float()).to(cq_out.dtype))
+    if q_rank:
+        cq_out.copy_((a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps) * wq.float()).to(cq_out.dtype))
     c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * wkv.float()
     flat = slab.view(-1, slab.shape[3])
     for t in range(p.shape[0]):
@@ -543,7 +548,93 @@ def mlstm_output(o32, nq, m, gates, norm_weight, eps, out):
     out.copy_(y.to(out.dtype))
 
 
-ALL = ["short_conv", "depth_mix", "moe_gather_scaled", "relu2_", "latent_store", "latent_query_rotate", "mlstm_gates", "mlstm_output", "linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
+def hyper_step(streams, init_from=None, y=None, mix=None, out_w=None, in_w=None, norm_w=None, eps=0.0, h_out=None,
+               sum_out=None):
+    S = streams.shape[0]
+    x = streams.float().clone()
+    if init_from is not None:
+        x = init_from.float()[None].expand(S, -1, -1).clone()
+    if y is not None:
+        x = torch.einsum("st,snc->tnc", mix.float(), x) + out_w.float()[:, None, None] * y.float()[None]
+    if init_from is not None or y is not None:
+        streams.copy_(x)
+    if in_w is not None:
+        u = torch.einsum("s,snc->nc", in_w.float(), x)
+        h_out.copy_((u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * norm_w.float()).to(h_out.dtype))
+    if sum_out is not None:
+        sum_out.copy_(x.sum(0))
+
+
+def norm_mean(xs, ws, eps, out):
+    acc = 0
+    for x, w in zip(xs, ws):
+        v = x.float()
+        acc = acc + v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.float()
+    out.copy_((acc / len(xs)).to(out.dtype))
+
+
+def conv_act(x, w, bias, act, state, state_slots, seg_info, n_segs, out):
+    """Per request: the step's inputs behind the slot's last ones; every output is the taps' sum (+ bias), activated."""
+    taps = w.shape[1]
+    keep = taps - 1
+    for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
+        slot = int(state_slots[i])
+        rows = x[q_start:q_start + q_len].float()
+        if keep:
+            old = torch.zeros(keep, x.shape[1]) if kv_len == q_len else state[slot].clone().float()
+            line = torch.cat([old, rows])
+        else:
+            line = rows
+        y = torch.zeros_like(rows)
+        for j in range(taps):
+            y = y + w[:, j].float() * line[j:j + q_len]
+        if bias is not None:
+            y = y + bias.float()
+        if act == "silu":
+            y = y * torch.sigmoid(y)
+        out[q_start:q_start + q_len] = y.to(out.dtype)
+        if keep:
+            state[slot] = line[-keep:]
+
+
+def ssm_gates(dt_raw, dt_bias, a_log, dt_out, decay_out):
+    dt = torch.nn.functional.softplus(dt_raw.float() + dt_bias.float(), threshold=1e9)
+    dt_out.copy_(dt)
+    decay_out.copy_(torch.exp(-torch.exp(a_log.float()) * dt))
+
+
+def ssm_output(o32, x, d_skip, z, norm_weight, norm_groups, eps, out):
+    T, H, P = o32.shape
+    zz = z.float()
+    y = (o32.float() + d_skip.float()[None, :, None] * x.float().view(T, H, P)).reshape(T, H * P) * (zz * torch.sigmoid(zz))
+    y = y.view(T, norm_groups, -1)
+    y = (y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps)).reshape(T, H * P) * norm_weight.float()
+    out.copy_(y.to(out.dtype))
+
+
+def delta_scan(q, k, v, b_raw, a_raw, a_log, dt_bias, q_scale, unit_eps, state, state_slots, seg_info, n_segs, out):
+    T, H, Dv = out.shape
+    D = state.shape[2]
+    G = q.shape[1] // D
+    qq, kk = q.float().view(T, G, D), k.float().view(T, G, D)
+    qq = qq * torch.rsqrt((qq * qq).sum(-1, keepdim=True) + unit_eps) * q_scale
+    kk = kk * torch.rsqrt((kk * kk).sum(-1, keepdim=True) + unit_eps)
+    qq, kk = qq.repeat_interleave(H // G, dim=1), kk.repeat_interleave(H // G, dim=1)
+    vv = v.float().view(T, H, Dv)
+    beta = torch.sigmoid(b_raw.float())
+    g = torch.exp(-torch.exp(a_log.float()) * torch.nn.functional.softplus(a_raw.float() + dt_bias.float(), threshold=1e9))
+    for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
+        slot = int(state_slots[i])
+        S = torch.zeros(H, D, Dv) if kv_len == q_len else state[slot].clone()
+        for t in range(q_start, q_start + q_len):
+            S = g[t][:, None, None] * S
+            u = beta[t][:, None] * (vv[t] - torch.einsum("hdv,hd->hv", S, kk[t]))
+            S = S + kk[t][:, :, None] * u[:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qq[t])
+        state[slot] = S
+
+
+ALL = ["hyper_step", "norm_mean", "conv_act", "ssm_gates", "ssm_output", "delta_scan", "short_conv", "depth_mix", "moe_gather_scaled", "relu2_", "latent_store", "latent_query_rotate", "mlstm_gates", "mlstm_output", "linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",
        "paged_attention", "router_topk", "moe_permute", "moe_route", "moe_route_fits", "linear", "attention_tc_fits", "attention_tc_few_fits", "moe_gemm1_gather_fits", "moe_gather", "moe_gemm1_act", "moe_gemm2",
        "moe_combine", "sample"]
 
