@@ -132,7 +132,43 @@ int ftk_gla_scan(const void* q, long long q_stride, const void* k, long long k_s
                  float* state, int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs,
                  const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, int any_single, int any_multi,
                  float* carry, float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
-                 const float* k_fac, const float* a_head, int ones_col, float* out_ones, void* stream);
+                 const float* k_fac, const float* a_head, int ones_col, float* out_ones, int qk_div, void* stream);
+// (qk_div > 1: head h reads the queries and keys of head h / qk_div, and q, k hold n_heads / qk_div heads; with a_head)
+
+// One pass over S <= 8 residual streams (hyper.cu), streams [S][T, C] float32, stream_stride floats apart; each step
+// optional, in this order: every stream = init_from [T, C]; x_t <- sum_s mix[s * S + t] x_s + out_w[t] y (y [T, C]
+// of y_dtype); h_out [T, C] of h_dtype = unit(sum_s in_w[s] x_s) * norm_w (division by the root mean square, eps
+// inside the root); sum_out [T, C] float32 = sum_s x_s.  All sums 32-bit.
+int ftk_hyper_step(float* streams, long long stream_stride, int n_streams, int n_tokens, int channels,
+                   const float* init_from, const void* y, int y_dtype, const float* mix, const float* out_w,
+                   const float* in_w, const float* norm_w, float eps, void* h_out, int h_dtype, float* sum_out,
+                   void* stream);
+// out = (1 / n) sum_i unit(xs[i]) * ws[i]: n <= 4 inputs [T, C] of `dtype`, float32 weights [C] (hyper.cu).
+// xs and ws are host arrays of four device pointers.
+int ftk_norm_mean(const void* const* xs, const float* const* ws, int n, int dtype, float eps, void* out, int n_tokens,
+                  int channels, void* stream);
+// Causal convolution over time per channel on rows of `dtype` (x rows x_stride elements apart), optional bias and
+// activation (0 none, 1 silu), per-request state of the last taps - 1 inputs as in ftk_short_conv (ssm.cu).
+int ftk_conv_act(const void* x, long long x_stride, int dtype, const float* w, const float* bias, int taps, int act,
+                 float* state, int n_slots, const int32_t* state_slots, const int32_t* seg_info, int n_segs, void* out,
+                 int n_tokens, int channels, void* stream);
+// dt_out = softplus(dt + dt_bias), decay_out = exp(-exp(a_log) * dt_out), [T, H] float32 (ssm.cu).
+int ftk_ssm_gates(const void* dt, long long dt_stride, int dtype, const float* dt_bias, const float* a_log, float* dt_out,
+                  float* decay_out, int n_tokens, int n_heads, void* stream);
+// out [T, H * P] = groupnorm((o32 + d_skip[h] * x) * silu(z)) * norm_w: norm_groups equal parts of a row, each divided
+// by its root mean square (ssm.cu).
+int ftk_ssm_output(const float* o32, const void* x, long long x_stride, const float* d_skip, const void* z,
+                   long long z_stride, int dtype, const float* norm_w, int norm_groups, float eps, void* out,
+                   int n_tokens, int n_heads, int vdim, void* stream);
+// Gated delta rule (delta.cu): per (segment, head) and token in order, S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+// o = S^T q, with beta = sigmoid(b), g = exp(-exp(a_log) softplus(a + dt_bias)), q and k made unit vectors per head
+// (x / sqrt(sum x^2 + unit_eps), q then times q_scale).  q, k hold n_kv_heads heads of `dim`; state [n_slots, n_heads,
+// dim, vdim] float32; out [T, n_heads, vdim] float32.
+int ftk_delta_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                   const void* b, long long b_stride, const void* a, long long a_stride, int dtype, const float* a_log,
+                   const float* dt_bias, float q_scale, float unit_eps, float* state, int n_slots,
+                   const int32_t* state_slots, const int32_t* seg_info, int n_segs, float* out, int n_tokens,
+                   int n_heads, int n_kv_heads, int dim, int vdim, void* stream);
 // Short causal convolution over time with a residual (shortconv.cu): out[t, c] = x[t, c] + sum_j w[c, j] *
 // in(t - taps + 1 + j, c) over the request's own inputs; the last taps - 1 inputs of every request live in its
 // state slot (state [n_slots, taps - 1, channels] float32, oldest first; zeros before the sequence's start) and are

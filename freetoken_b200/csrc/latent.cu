@@ -49,7 +49,7 @@ __global__ void latent_store_kernel(const T* __restrict__ proj, long long row_st
   }
   sq = block_sum(sq, scratch);
   skv = block_sum(skv, scratch);
-  const float rq = rsqrtf(sq / (float)q_rank + eps), rkv = rsqrtf(skv / (float)kv_rank + eps);
+  const float rq = q_rank ? rsqrtf(sq / (float)q_rank + eps) : 0.f, rkv = rsqrtf(skv / (float)kv_rank + eps);
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
     cq_out[(size_t)t * q_rank + i] = from_float<T>(row[i] * rq * wq[i]);
   const long long slot = slot_map[t];
@@ -142,10 +142,10 @@ extern "C" int ftk_latent_store(const void* proj, int dtype, long long row_strid
                                 const int32_t* positions, const float* table, int max_pos, void* cq_out, void* slab,
                                 long long slab_rows, const int32_t* slot_map, int pad_dim, int n_tokens, void* stream) {
   FTK_REQUIRE(dtype_ok(dtype), "latent_store: bad dtype %d", dtype);
-  FTK_REQUIRE(q_rank >= 1 && kv_rank >= 1 && rot_dim >= 0 && n_rot >= 0 && n_rot <= rot_dim && n_rot % 2 == 0 &&
+  FTK_REQUIRE(q_rank >= 0 && kv_rank >= 1 && rot_dim >= 0 && n_rot >= 0 && n_rot <= rot_dim && n_rot % 2 == 0 &&
               pad_dim >= kv_rank + rot_dim && n_tokens >= 0, "latent_store: bad sizes");
   if (n_tokens == 0) return 0;
-  FTK_REQUIRE(proj && wq && wkv && positions && cq_out && slab && slot_map && (n_rot == 0 || table),
+  FTK_REQUIRE(proj && (q_rank == 0 || (wq && cq_out)) && wkv && positions && slab && slot_map && (n_rot == 0 || table),
               "latent_store: null pointer");
   const int width = q_rank + kv_rank + rot_dim;
   const size_t smem = (size_t)(width + 33) * sizeof(float);

@@ -55,6 +55,7 @@ struct GlaArgs {
   const float* a_head;     // [T, H] or null: one decay per (token, head) for all key channels, in place of z
   int ones_col;            // 1: the last of the Dv value columns is 1 for every token, and v holds Dv - 1 columns per head
   float* out_ones;         // [T, H] or null: with ones_col, that column's outputs go here and out is [T, H, Dv - 1]
+  int qk_div;              // queries and keys are shared by groups of this many heads: head h reads q/k head h / qk_div
 };
 
 // 16 bytes from global to shared memory without a trip through registers; `valid` false writes zeros
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
   float* sv = sa + kGlaBatch * Dp;              // [batch][cols]
   float* part = sv + kGlaBatch * cols;          // [slices][batch][cols]
   const int c = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
+  const int hqk = h / a.qk_div;
   const int32_t* ch = a.chunks + (size_t)c * 4;
   const int seg = ch[0], tok0 = ch[1], ntok = ch[2], place = ch[3];
   if (seg < 0 || seg >= a.n_segs || ntok <= 0) return;
@@ -176,8 +178,8 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
       const int t = i / per_row, d = (i % per_row) * 8;
       const size_t tok = (size_t)(q_start + tok0 + b0n + t);
       const bool in = d < D;
-      gla_cp16(kraw + t * Dp + d, in ? kg + tok * a.k_stride + (size_t)h * D + d : kg, in);
-      if (MODE != 1) gla_cp16(qraw + t * Dp + d, in ? qg + tok * a.q_stride + (size_t)h * D + d : qg, in);
+      gla_cp16(kraw + t * Dp + d, in ? kg + tok * a.k_stride + (size_t)hqk * D + d : kg, in);
+      if (MODE != 1) gla_cp16(qraw + t * Dp + d, in ? qg + tok * a.q_stride + (size_t)hqk * D + d : qg, in);
       if (!a.a_head) {
         const float* zr = in ? a.z + (tok * a.H + h) * D + d : a.z;
         gla_cp16(zraw + t * Dp + d, zr, in);
@@ -252,14 +254,14 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
 #pragma unroll
         for (int u = 0; u < 8; ++u) { qv[u] = 0.f; kv[u] = 0.f; av[u] = 1.f; }
         if (d < D) {
-          const uint4 kr = *reinterpret_cast<const uint4*>(kb + tok * a.k_stride + (size_t)h * D + d);
+          const uint4 kr = *reinterpret_cast<const uint4*>(kb + tok * a.k_stride + (size_t)hqk * D + d);
           const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kr);
 #pragma unroll
           const float kf = a.k_fac ? a.k_fac[tok * a.H + h] : 1.f;
 #pragma unroll
           for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(k2[u]); kv[2 * u] = f.x * kf; kv[2 * u + 1] = f.y * kf; }
           if (MODE != 1) {
-            const uint4 qr = *reinterpret_cast<const uint4*>(qb + tok * a.q_stride + (size_t)h * D + d);
+            const uint4 qr = *reinterpret_cast<const uint4*>(qb + tok * a.q_stride + (size_t)hqk * D + d);
             const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qr);
 #pragma unroll
             for (int u = 0; u < 4; ++u) { const float2 f = __bfloat1622float2(q2[u]); qv[2 * u] = f.x * a.q_scale; qv[2 * u + 1] = f.y * a.q_scale; }
@@ -292,8 +294,8 @@ __global__ void __launch_bounds__(gla_max_groups(DPT) * kGlaSlices * 32) gla_chu
         const size_t tok = (size_t)(q_start + tok0 + b0 + t);
         float qv = 0.f, kv = 0.f, av = 1.f;
         if (d < D) {
-          if (MODE != 1) qv = to_float(qb[tok * a.q_stride + (size_t)h * D + d]) * a.q_scale;
-          kv = to_float(kb[tok * a.k_stride + (size_t)h * D + d]) * (a.k_fac ? a.k_fac[tok * a.H + h] : 1.f);
+          if (MODE != 1) qv = to_float(qb[tok * a.q_stride + (size_t)hqk * D + d]) * a.q_scale;
+          kv = to_float(kb[tok * a.k_stride + (size_t)hqk * D + d]) * (a.k_fac ? a.k_fac[tok * a.H + h] : 1.f);
           av = a.a_head ? a.a_head[tok * a.H + h] : a.z[(tok * a.H + h) * D + d];
           if (!a.a_head && !a.z_is_decay) av = decay_of(av + (a.z_bias ? a.z_bias[(size_t)h * D + d] : 0.f), a.inv_tau);
         }
@@ -488,7 +490,8 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
                             const int32_t* seg_info, int n_segs, const int32_t* chunks, int n_chunks,
                             const int32_t* seg_chunks, int any_single, int any_multi, float* carry,
                             float* decay_prod, float* out, int n_tokens, int n_heads, int dim, int vdim,
-                            const float* k_fac, const float* a_head, int ones_col, float* out_ones, void* stream) {
+                            const float* k_fac, const float* a_head, int ones_col, float* out_ones, int qk_div,
+                            void* stream) {
   FTK_REQUIRE(dtype_ok(dtype), "gla_scan: bad dtype %d", dtype);
   FTK_REQUIRE(n_tokens >= 0 && n_segs >= 0 && n_chunks >= 0, "gla_scan: bad counts");
   if (n_tokens == 0 || n_chunks == 0) return 0;
@@ -507,7 +510,9 @@ extern "C" int ftk_gla_scan(const void* q, long long q_stride, const void* k, lo
   a.state = state; a.state_slots = state_slots; a.seg_info = seg_info; a.chunks = chunks; a.seg_chunks = seg_chunks;
   a.n_chunks = n_chunks; a.n_segs = n_segs; a.n_slots = n_slots; a.carry = carry; a.decay_prod = decay_prod;
   FTK_REQUIRE(!out_ones || ones_col, "gla_scan: outputs of a column of ones that is not there");
-  a.k_fac = k_fac; a.a_head = a_head; a.ones_col = ones_col; a.out_ones = out_ones;
+  FTK_REQUIRE(qk_div >= 1 && n_heads % qk_div == 0 && (qk_div == 1 || a_head),
+              "gla_scan: heads that share queries and keys come in groups that divide the heads, with a decay per head");
+  a.k_fac = k_fac; a.a_head = a_head; a.ones_col = ones_col; a.out_ones = out_ones; a.qk_div = qk_div;
   a.out = out; a.H = n_heads; a.D = dim; a.Dv = vdim; a.n_tokens = n_tokens;
   cudaStream_t s = (cudaStream_t)stream;
   note_variant(any_multi ? "gla_scan: chunks side by side" : "gla_scan: one chunk per request");

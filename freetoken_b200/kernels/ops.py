@@ -1197,7 +1197,8 @@ def latent_store(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, n_
     ``rope_table [positions, n_rot]`` (``cos || sin``).  A token whose slot is negative stores nothing."""
     T = proj.shape[0]
     width = q_rank + kv_rank + rot_dim
-    if proj.shape != (T, width) or proj.stride(1) != 1 or cq_out.shape != (T, q_rank) or not cq_out.is_contiguous():
+    if proj.shape != (T, width) or proj.stride(1) != 1 or not proj.is_cuda or cq_out.shape != (T, q_rank) \
+            or not cq_out.is_contiguous():
         raise KernelError("latent_store: proj [T, q_rank + kv_rank + rot_dim], cq_out [T, q_rank] expected")
     if slab.dim() != 4 or slab.shape[1] != 1 or slab.shape[3] < kv_rank + rot_dim or slab.dtype != proj.dtype \
             or cq_out.dtype != proj.dtype or not slab.is_contiguous():
@@ -1205,7 +1206,7 @@ def latent_store(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, n_
     if n_rot and (rope_table is None or rope_table.shape[1] != n_rot):
         raise KernelError("latent_store: the rotation table must be [positions, n_rot]")
     _check(_lib().ftk_latent_store(
-        _dev(proj, "proj"), _code(proj, "proj"), proj.stride(0) if T > 1 else width, q_rank, kv_rank, rot_dim, n_rot,
+        proj.data_ptr(), _code(proj, "proj"), proj.stride(0) if T > 1 else width, q_rank, kv_rank, rot_dim, n_rot,
         1 if interleaved else 0, _dev(wq, "wq", torch.float32), _dev(wkv, "wkv", torch.float32), float(eps),
         _dev(positions, "positions", torch.int32), _dev(rope_table, "rope_table", torch.float32),
         rope_table.shape[0] if rope_table is not None else 1, _dev(cq_out, "cq_out"), _dev(slab, "slab"),
