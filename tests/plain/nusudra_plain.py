@@ -236,3 +236,12 @@ class PlainNusudra:
         if S:
             x = sum(xs)
         return (unit(x, eps) * w["final.norm"]) @ w["head"].T
+
+    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        return self.forward(tokens).float()
+
+    def layer_sums(self, tokens: Sequence[int]) -> List[torch.Tensor]:
+        """The stream (the sum of the copies) after every layer, float32."""
+        out: List[torch.Tensor] = []
+        self.forward(tokens, out)
+        return [x.float() for x in out]
