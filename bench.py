@@ -21,7 +21,7 @@ of the whole batch.  It prints ONE JSON line:
 
 ``--workload long_contexts | chunked_prefill`` runs one of the larger workloads of
 freetoken_b200/workloads.py instead and prints that workload's own JSON line; ``--workload designs`` times
-the Rumalorn, Pabavik and Kekopel designs beside MiniMax-M3 at equal layer sizes (prefill and decode, a few sizes).
+the Rumalorn, Pabavik, Kekopel and Nusudra designs beside MiniMax-M3 at equal layer sizes (prefill and decode, a few sizes).
 
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else 6.65 TB/s and 1.59 PFLOP/s.
 More than one GPU is outside this engine: ``--gpus N`` with N > 1 prints one line and exits 2.
@@ -197,7 +197,7 @@ def main():
         from freetoken_b200 import workloads
 
         layers = args.layers if "--layers" in sys.argv else None
-        if args.workload == "designs":  # Rumalorn, Pabavik and Kekopel beside MiniMax-M3 at equal layer sizes
+        if args.workload == "designs":  # Rumalorn, Pabavik, Kekopel and Nusudra beside MiniMax-M3 at equal layer sizes
             return workloads.run("designs", HEADLINE, layers=layers, steps=args.steps if "--steps" in sys.argv else None,
                                  only=args.designs)
         if args.workload == "long_contexts":

@@ -1024,7 +1024,7 @@ static int paged_attention_tc_impl(const void* q, const void* k_slab, const void
   p.has_sink = extras ? extras->has_sink : 0;
   p.sink = extras ? extras->sink_logit : 0.f;
   p.sink_heads = extras ? extras->sink_heads : nullptr;
-  FTK_REQUIRE(!p.has_sink || (form == kTcSingle && !p.dist_bias),
+  FTK_REQUIRE(!p.has_sink || form == kTcSingle,
               "paged_attention_tc: of the tcgen05 kernels the one with 128-row tiles takes a softmax sink");
   cudaStream_t s = (cudaStream_t)stream;
   if (p.dist_bias) note_variant(few ? "attention: tcgen05, tiles of at most 16 rows, bias by distance"

@@ -14,6 +14,8 @@
     python -m freetoken_b200.kernels.microbench gla --batch 8
     python -m freetoken_b200.kernels.microbench kekopel --tokens 2048 [--batch 8]
     python -m freetoken_b200.kernels.microbench attention --prefill 2048 --tied --kv-heads 1 --window 1024 --head-sinks
+    python -m freetoken_b200.kernels.microbench nusudra --tokens 2048 [--batch 8]
+    python -m freetoken_b200.kernels.microbench attention --prefill 2048 --dist-bias 2048 --head-sinks
 
 Each case allocates its inputs once (larger than L2 where the real workload is), warms up, then
 times ``--iters`` launches with CUDA events and prints one JSON line: time, the bytes the kernel has
@@ -384,6 +386,112 @@ def bench_kekopel(a) -> dict:
     return results
 
 
+def bench_nusudra(a) -> dict:
+    """The kernels that the Nusudra layers add around the library products: the pass over the residual streams
+    (write a sub-layer's result, read for the next one, norm), the token shift, the mean of the normed branches, the
+    convolution of projected rows, the state-space layer's gates, recurrence (queries and keys shared by groups of
+    heads) and output, and the delta rule.  Attention with a bias by distance and a sink per head is
+    ``attention --dist-bias L --head-sinks``."""
+    from ..parts.gla import chunk_list
+
+    dev = "cuda"
+    T, C, H, D, Dv, S = a.tokens, a.hidden, a.heads, a.head_dim, a.vdim, a.streams
+    decode = a.batch > 0
+    segs = [(1, a.context)] * a.batch if decode else [(T, T)]
+    T = sum(q for q, _ in segs)
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf, f32 = torch.bfloat16, torch.float32
+    info, q0 = [], 0
+    for ql, kv in segs:
+        info.append([q0, ql, kv, 0])
+        q0 += ql
+    seg = torch.tensor(info, dtype=torch.int32, device=dev)
+    slots = torch.arange(1, len(segs) + 1, dtype=torch.int32, device=dev)
+    n_slots = len(segs) + 1
+    results = {}
+    fp32_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+
+    def add(name, fn, nbytes, flops=0):
+        us = _time(fn, a.iters, a.warmup, a.profile)
+        results[name] = {"us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1),
+                         "hbm_frac": round(nbytes / us / 1e3 / HBM_GBS, 3)}
+        if flops:
+            results[name].update(flops=flops, tflops=round(flops / us / 1e6, 2),
+                                 fp32_frac_nominal=round(flops / us / 1e6 / fp32_tflops, 3))
+
+    streams = torch.randn(S, T, C, device=dev, generator=g)
+    y = torch.randn(T, C, device=dev, generator=g).to(bf)
+    mix, ow, iw = torch.rand(S, S, device=dev, generator=g), torch.rand(S, device=dev, generator=g), torch.rand(S, device=dev, generator=g)
+    nw = torch.ones(C, device=dev)
+    h32, h = torch.empty(T, C, device=dev), torch.empty(T, C, dtype=bf, device=dev)
+    add(f"hyper_step (write, read and norm over {S} streams; 32-bit out)",
+        lambda: ops.hyper_step(streams, y=y, mix=mix, out_w=ow, in_w=iw, norm_w=nw, eps=1e-6, h_out=h32),
+        T * C * (2 * S * 4 + 2 + 4))
+    add(f"hyper_step (write, read and norm over {S} streams)",
+        lambda: ops.hyper_step(streams, y=y, mix=mix, out_w=ow, in_w=iw, norm_w=nw, eps=1e-6, h_out=h),
+        T * C * (2 * S * 4 + 2 + 2))
+    sw = torch.rand(C, 2, device=dev, generator=g)
+    sstate = torch.zeros(n_slots, 1, C, device=dev)
+    add("short_conv (token shift: two taps on the normed rows)",
+        lambda: ops.short_conv(h32, sw, sstate, slots, seg, len(segs), h), T * C * (4 + 2) + (2 * len(segs) * C * 4 if decode else 0))
+    y2 = torch.randn(T, C, device=dev, generator=g).to(bf)
+    add("norm_mean (two branches)", lambda: ops.norm_mean([y, y2], [nw, nw], 1e-6, h), T * C * 2 * 3)
+    # state space: inner = heads_ssm * 64, state N, groups
+    Hs, P, N, G, taps = a.ssm_heads, 64, a.state, a.groups, a.taps
+    inner, bc = Hs * P, G * N
+    proj = (torch.randn(T, 2 * inner + 2 * bc + Hs, device=dev, generator=g) * 0.5).to(bf)
+    cw = torch.randn(inner + 2 * bc, taps, device=dev, generator=g) * 0.3
+    cb = torch.zeros(inner + 2 * bc, device=dev)
+    cstate = torch.zeros(n_slots, taps - 1, inner + 2 * bc, device=dev)
+    xbc = torch.empty(T, inner + 2 * bc, dtype=bf, device=dev)
+    add("conv_act (bias, silu, on a view of the projection)",
+        lambda: ops.conv_act(proj[:, inner:2 * inner + 2 * bc], cw, cb, "silu", cstate, slots, seg, len(segs), xbc),
+        T * (inner + 2 * bc) * 4 + (2 * len(segs) * (taps - 1) * (inner + 2 * bc) * 4 if decode else 0))
+    dtb, alog = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev)
+    step, dec = torch.empty(T, Hs, device=dev), torch.empty(T, Hs, device=dev)
+    add("ssm_gates", lambda: ops.ssm_gates(proj[:, 2 * inner + 2 * bc:], dtb, alog, step, dec), T * Hs * (2 + 8))
+    chunks, per_seg, single, multi = chunk_list(segs, a.chunk)
+    n = chunks.shape[0]
+    state = torch.zeros(n_slots, Hs, N, P, device=dev)
+    carry = torch.empty(n, Hs, N, P, device=dev) if multi else None
+    decay = torch.empty(n, Hs, N, device=dev) if multi else None
+    o32 = torch.empty(T, Hs, P, device=dev)
+    cd, pd = torch.from_numpy(chunks).to(dev), torch.from_numpy(per_seg).to(dev)
+    passes = 2 if multi else 1
+    add("gla_scan (state space: keys times a step size, a decay per head, q and k shared by groups of heads)",
+        lambda: ops.gla_scan(xbc[:, inner + bc:], xbc[:, inner:inner + bc], xbc[:, :inner], None, None, 1.0, 1.0, state, slots,
+                             seg, len(segs), cd, n, pd, single, multi, carry, decay, o32, k_fac=step, a_head=dec,
+                             qk_div=Hs // G),
+        T * Hs * ((2 * N + P) * 2 + 8) * passes + T * Hs * P * 4 + (2 * len(segs) + (2 * n if multi else 0)) * Hs * N * P * 4,
+        T * Hs * N * P * (8 if multi else 5))
+    dsk, snw = torch.ones(Hs, device=dev), torch.ones(inner, device=dev)
+    yo = torch.empty(T, inner, dtype=bf, device=dev)
+    add("ssm_output (skip, gate, norm in groups)",
+        lambda: ops.ssm_output(o32, xbc[:, :inner], dsk, proj[:, :inner], snw, G, 1e-6, yo), T * inner * (4 + 2 * 3))
+    # delta rule
+    Gk = a.kv_heads
+    dproj = (torch.randn(T, 2 * Gk * D + 2 * H * Dv + 2 * H, device=dev, generator=g) * 0.5).to(bf)
+    dconv = 2 * Gk * D + H * Dv
+    dw = torch.randn(dconv, taps, device=dev, generator=g) * 0.3
+    dstate_c = torch.zeros(n_slots, taps - 1, dconv, device=dev)
+    qkv = torch.empty(T, dconv, dtype=bf, device=dev)
+    add("conv_act (no bias, silu: q, k, v of the delta rule)",
+        lambda: ops.conv_act(dproj[:, :dconv], dw, None, "silu", dstate_c, slots, seg, len(segs), qkv), T * dconv * 4)
+    dstate = torch.zeros(n_slots, H, D, Dv, device=dev)
+    do32 = torch.empty(T, H, Dv, device=dev)
+    al, db = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+    add("delta_scan",
+        lambda: ops.delta_scan(qkv[:, :Gk * D], qkv[:, Gk * D:2 * Gk * D], qkv[:, 2 * Gk * D:], dproj[:, -2 * H:-H], dproj[:, -H:],
+                               al, db, D ** -0.5, 1e-6, dstate, slots, seg, len(segs), do32),
+        T * H * ((2 * D + Dv) * 2 + 4) + T * H * Dv * 4 + 2 * len(segs) * H * D * Dv * 4, T * H * D * Dv * 6)
+    o = torch.empty(T, H, Dv, dtype=bf, device=dev)
+    hw = torch.ones(Dv, device=dev)
+    add("gated_heads (head norm, silu gate)",
+        lambda: ops.gated_heads(do32, dproj[:, dconv:dconv + H * Dv], o, Dv, "silu", hw, 1e-6), T * H * Dv * (4 + 2 + 2))
+    results["status"] = ops.read_status()
+    return results
+
+
 def bench_few(a) -> dict:
     """The few-token kernels (``csrc/gemv.cu``) at the headline sizes: the qkv and output projections of
     ``--tokens`` tokens, and the routed gate/up and down products of their routes.  Six copies of the dense
@@ -499,7 +607,7 @@ def bench_sample(a) -> dict:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="case", required=True)
-    for name in ("moe", "attention", "sample", "sparse", "few", "rows", "gla", "kekopel"):
+    for name in ("moe", "attention", "sample", "sparse", "few", "rows", "gla", "kekopel", "nusudra"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -555,6 +663,21 @@ def main(argv=None) -> int:
             p.add_argument("--taps", type=int, default=4)
             p.add_argument("--depth", type=int, default=3, help="outputs before this layer's that the mix reads")
             p.add_argument("--chunk", type=int, default=64)
+        elif name == "nusudra":
+            p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--batch", type=int, default=0, help="requests with one token each instead of one portion")
+            p.add_argument("--context", type=int, default=2048)
+            p.add_argument("--hidden", type=int, default=3072)
+            p.add_argument("--streams", type=int, default=4)
+            p.add_argument("--heads", type=int, default=48)
+            p.add_argument("--kv-heads", type=int, default=8)
+            p.add_argument("--head-dim", type=int, default=128)
+            p.add_argument("--vdim", type=int, default=128)
+            p.add_argument("--ssm-heads", type=int, default=48)
+            p.add_argument("--state", type=int, default=128)
+            p.add_argument("--groups", type=int, default=8)
+            p.add_argument("--taps", type=int, default=4)
+            p.add_argument("--chunk", type=int, default=64)
         elif name == "few":
             p.add_argument("--tokens", type=int, default=1)
             p.add_argument("--hidden", type=int, default=3072)
@@ -592,7 +715,7 @@ def main(argv=None) -> int:
             p.add_argument("--temperature", type=float, default=0.0)
     a = ap.parse_args(argv)
     res = {"moe": bench_moe, "attention": bench_attention, "sample": bench_sample, "sparse": bench_sparse, "few": bench_few,
-           "rows": bench_rows, "gla": bench_gla, "kekopel": bench_kekopel}[a.case](a)
+           "rows": bench_rows, "gla": bench_gla, "kekopel": bench_kekopel, "nusudra": bench_nusudra}[a.case](a)
     print(json.dumps({"case": a.case, **{k: v for k, v in vars(a).items() if k != "case"}, "result": res}))
     return 0
 

@@ -466,7 +466,7 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
     also holds ``e^sink``, a key without a value, so a row's weights are ``e^(s_j) / (e^sink + sum_i e^(s_i))``.  A tile that is split along the keys gets it once,
     in the merge.  Not with block selection.  Of the tcgen05 kernels the one with 128-row tiles takes a window and a
     sink (its work list then starts every piece on a key tile: ``build_plan(..., window, key_tile=128)``), also with
-    one slab for keys and values.
+    one slab for keys and values, and a sink together with a bias by distance.
     """
     T, Hq, D = q.shape
     pages, Hkv, P, D2 = k_slab.shape
@@ -493,11 +493,17 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
         # bfloat16 steps on the tcgen05 kernels: one query tile per CTA, a pair of them, or tiles of a few rows
         if sel is not None or q.dtype != torch.bfloat16:
             raise KernelError("paged_attention: the tcgen05 kernels take bfloat16 without block selection")
-        if window or sink is not None:  # the form with one 128-row query tile a piece takes both
-            if tile_rows != 128 or few_rows or dist_bias is not None:
-                raise KernelError("paged_attention: of the tcgen05 kernels the one with 128-row tiles takes a window or a "
-                                  "sink (no distance bias)")
-            ex = _AttnExtras(None, 0, 1, 0 if sink is None else 1, 0.0 if sink is None else float(sink), sink_heads)
+        if window or sink is not None or dist_bias is not None:
+            # the form with one 128-row query tile a piece takes a window, a sink and a bias by distance (a bias not
+            # together with a window); the form for tiles of at most 16 rows takes the bias alone
+            if (window or sink is not None) and (tile_rows != 128 or few_rows):
+                raise KernelError("paged_attention: of the tcgen05 kernels the one with 128-row tiles takes a window or a sink")
+            if dist_bias is not None and (tile_rows == 256 or window or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq):
+                raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "
+                                  "distance bias [Hq, L] (no window)")
+            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1] if dist_bias is not None else 0,
+                             1, 0 if sink is None else 1, 0.0 if sink is None else float(sink), sink_heads)
+            what = "distance bias" if dist_bias is not None else "window or sink"
             _check(_lib().ftk_paged_attention_tc_ex(
                 _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
                 _dev(block_table, "block_table", torch.int32), block_table.shape[1],
@@ -505,23 +511,8 @@ def paged_attention(q: torch.Tensor, k_slab: torch.Tensor, v_slab: torch.Tensor,
                 _dev(items, "items", torch.int32), n_items,
                 _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
                 _dev(out, "out"), T, Hq, Hkv, D, P, pages, float(scale), int(window) if window else 0, ctypes.byref(ex),
-                0, _stream()),
-                "paged_attention (tcgen05, window or sink)", 2 if n_slots else 1)
-            return
-        if dist_bias is not None:  # the forms with one query tile a piece (128 rows, or at most 16) take it
-            if tile_rows == 256 or dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
-                raise KernelError("paged_attention: of the tcgen05 kernels the ones with one query tile a piece take a "
-                                  "distance bias [Hq, L]")
-            ex = _AttnExtras(_dev(dist_bias, "dist_bias", torch.float32), dist_bias.shape[1], 1, 0, 0.0, None)
-            _check(_lib().ftk_paged_attention_tc_ex(
-                _dev(q, "q"), _dev(k_slab, "k_slab"), _dev(v_slab, "v_slab"),
-                _dev(block_table, "block_table", torch.int32), block_table.shape[1],
-                _dev(seg_info, "seg_info", torch.int32), n_segs,
-                _dev(items, "items", torch.int32), n_items,
-                _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), n_slots,
-                _dev(out, "out"), T, Hq, Hkv, D, P, pages, float(scale), 0, ctypes.byref(ex), 1 if few_rows else 0,
-                _stream()),
-                "paged_attention (tcgen05, distance bias)", 2 if n_slots else 1)
+                1 if few_rows else 0, _stream()),
+                f"paged_attention (tcgen05, {what})", 2 if n_slots else 1)
             return
         fn = (_lib().ftk_paged_attention_tc_few if few_rows else
               _lib().ftk_paged_attention_tc_pair if tile_rows == 256 else _lib().ftk_paged_attention_tc)

@@ -223,8 +223,6 @@ class GQAttention(Mixer):
         # (the tcgen05 kernels take no split KV heads; a sink or a window goes with the 128-row form alone)
         sized = self.kv_split == 1
         has_sink = self.sink is not None or self.learned_sink
-        if has_sink and self.log_dist_bias:  # (a sink together with a bias by distance: the tiles of 16 / 64 rows take both)
-            sized = False
         special = has_sink or self.window is not None
         return attention_kernel_form(self.env.dtype, decode_only, self.plan_group, n_tokens,
                                      self.pad_dim if sized else 0, page_size, self.window, longest_span,

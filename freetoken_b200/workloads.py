@@ -178,7 +178,19 @@ def _design_configs(width, heads, kv, dim, experts, top, ff, vocab, layers):
     keko = {"architecture": "Kekopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
             "layers": [{"type": "mlstm" if i % 3 == 2 else "latent_attention", "mixer": dict(mem if i % 3 == 2 else lat),
                         "mlp": kmlp[i % 2]} for i in range(layers)]}
-    return {"rumalorn": ruma, "pabavik": paba, "kekopel": keko, "minimax_m3": m3}
+    # Nusudra: latent attention (no query latent, a gate per head; the same cached rows as Kekopel's, no window), softmax
+    # attention with biases, a bias by the logarithm of the distance and a sink per head beside a Mamba-2 layer, and the
+    # gated delta rule, in turns; four residual streams, token shift, dense feed-forwards as wide as a token's experts
+    nlat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+            "rot": {"dims": rot, "base": 1000000.0}}
+    pair = {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5},
+            "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": kv, "conv": 4, "norm_groups": kv}}
+    delta = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "conv": 4}
+    kinds = [("latent_attention", nlat), ("parallel", pair), ("delta", delta)]
+    nusu = {"architecture": "Nusudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "streams": 4, "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1],
+                                      "mlp": {"kind": "dense", "ff": top * ff}} for i in range(layers)]}
+    return {"rumalorn": ruma, "pabavik": paba, "kekopel": keko, "nusudra": nusu, "minimax_m3": m3}
 
 
 def _time_design(raw: Dict[str, Any], prompt: int, batch: int, steps: int, warmup: int) -> Dict[str, Any]:
@@ -248,7 +260,7 @@ def designs(raw: Dict[str, Any], layers: int = 4, prompt: int = 2048, batch: int
             row[design] = _time_design(cfg, prompt, batch, steps, warmup)
             gc.collect()
             torch.cuda.empty_cache()
-        for design in ("rumalorn", "pabavik", "kekopel"):
+        for design in ("rumalorn", "pabavik", "kekopel", "nusudra"):
             if design not in row:
                 continue
             row[f"{design}_over_minimax_m3"] = {

@@ -267,6 +267,8 @@ def test_a_value_written_once_is_read_hundreds_of_tokens_later(cuts):
 def run_biased(dtype, Hq, Hkv, D, P, lens, tile, r1, r2, sink, scale, problem=None, force_split=False):
     q, ks, vs, bt, seg = problem or attention_problem(dtype, Hq, Hkv, D, P, lens)
     kw = dict(sm_count=4096, min_split_keys=32) if force_split else dict(sm_count=148)
+    if tile == 128:
+        kw["key_tile"] = 128  # as the engine plans the tcgen05 kernel's work
     plan = build_plan(lens, Hq // Hkv, tile, None, Hkv, **kw)
     items = torch.from_numpy(plan.items).to(DEV)
     part_o = part_ml = None
@@ -296,6 +298,22 @@ def test_attention_with_a_log_distance_bias_and_a_sink_per_head(dtype, Hq, Hkv, 
     for tile in ([16] if dtype == torch.float32 else [16, 64]):
         out, want, _ = run_biased(dtype, Hq, Hkv, D, P, lens, tile, r1, r2, sink, 0.8 * D ** -0.5, force_split=split)
         torch.testing.assert_close(out.float().cpu(), want.float().cpu(), **attn_tol(dtype))
+
+
+@pytest.mark.parametrize("Hq,Hkv,P,split", [(4, 4, 16, False), (8, 2, 16, True), (16, 1, 32, False), (6, 3, 64, True)])
+def test_the_tensor_core_kernel_takes_the_bias_and_the_sink_together(Hq, Hkv, P, split):
+    """Heads of 128 in steps of 128 tokens and more: long portions, portions behind hundreds of cached tokens, tiles cut
+    along the keys (the sink then joins in the merge), beside single tokens."""
+    lens = [(300, 300), (130, 700), (1, 64), (128, 128), (2, 515)]
+    r1 = torch.rand(Hq, generator=torch.Generator().manual_seed(1)) + 0.2
+    r2 = torch.rand(Hq, generator=torch.Generator().manual_seed(2)) + 0.05
+    sink = rnd(Hq, seed=3) + 1.0
+    ops.variant_counts(reset=True)
+    out, want, _ = run_biased(torch.bfloat16, Hq, Hkv, 128, P, lens, 128, r1, r2, sink, 0.8 * 128 ** -0.5, force_split=split)
+    assert ops.variant_counts().get("attention: tcgen05, 128-row query tiles, bias by distance", 0) == 1
+    torch.testing.assert_close(out.float().cpu(), want.float().cpu(), **attn_tol(torch.bfloat16))
+    no_sink, _, _ = run_biased(torch.bfloat16, Hq, Hkv, 128, P, lens, 128, r1, r2, None, 0.8 * 128 ** -0.5, force_split=split)
+    assert float((no_sink.float() - out.float()).abs().max()) > 0.05  # the sink is not lost on the way
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
