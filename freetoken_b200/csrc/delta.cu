@@ -5,17 +5,23 @@
 // (x / sqrt(sum x^2 + eps)), q also scaled.  State, gates, norms and all sums are 32-bit.
 //
 // The correction u needs S^T k of the state as the token finds it, so a request's tokens run one after the other.
-// What runs side by side are the state's columns: a block owns 32 value columns of one (request, head); four
-// neighbouring lanes share a column, each keeping a quarter of its key channels in registers, so that S^T k and
-// S^T q are a thread's own sums plus two shuffles and no thread waits for another warp.  The tokens' q, k (normed
-// as they are staged), v and gates come through shared memory 16 tokens at a time; the outputs of a batch leave
-// together.  A decode step is the same kernel with one token per request.
+// What runs side by side are the state's columns: a block owns 16 value columns of one (request, head); eight
+// neighbouring lanes share a column, each keeping an eighth of its key channels in registers (the kernel is bound
+// by the latency of a token's chain of sums, shuffles and updates, so many short chains in many warps beat few
+// long ones).  One pass over a thread's share of the state gives both S^T k and S^T q of the state as found (three
+// shuffles each, interleaved), and the token's output follows without a second pass: with r = S^T k, p = S^T q of
+// the state before the decay,
+//   u = beta (v - g r),   o = g p + (k . q) u,   S <- g S + k u^T.
+// The tokens' q, k, v come through shared memory 16 tokens at a time: rows that allow 16-byte copies are fetched a
+// batch ahead with cp.async as they lie in memory while the current batch runs, and a pass from shared to shared
+// memory widens them, makes q and k unit vectors (eight lanes a token) and takes k . q; every slice's channels are
+// set off by 16 bytes (and every raw row by 16 bytes) so that lanes that read side by side fall into different
+// banks.  The outputs of a batch leave together.  A decode step is the same kernel with one token per request.
 #include "common.cuh"
 
 namespace ftk {
 
 constexpr int kDeltaBatch = 16;   // tokens staged at a time
-constexpr int kDeltaCols = 32;    // value columns per block
 constexpr int kDeltaThreads = 128;
 
 struct DeltaArgs {
@@ -26,20 +32,49 @@ struct DeltaArgs {
   float* state; int n_slots;
   const int32_t* state_slots; const int32_t* seg_info; int n_segs;
   float* out; int n_tokens, H, G, D, Dv;
+  int wide;  // q, k and v rows allow 16-byte copies
 };
 
 __device__ __forceinline__ float delta_softplus(float z) { return z > 0.f ? z + log1pf(expf(-z)) : log1pf(expf(z)); }
+__device__ __forceinline__ void delta_cp16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;  // fewer source bytes than 16: the rest is written as zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void delta_cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void delta_cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
-template <typename T, int DPT>
+// DPT key channels a thread, LPC lanes a column
+template <int DPT, int LPC>
+__host__ __device__ constexpr int delta_row_len() { return DPT * LPC + 4 * LPC; }  // a slice's channels start 16 bytes behind the slice before
+template <int LPC>
+__host__ __device__ constexpr int delta_cols() { return kDeltaThreads / LPC; }  // value columns per block
+template <typename T, int DPT, int LPC>
+__host__ __device__ constexpr size_t delta_smem_bytes() {
+  return ((size_t)2 * kDeltaBatch * delta_row_len<DPT, LPC>() + 2 * kDeltaBatch * delta_cols<LPC>() + 3 * kDeltaBatch) * sizeof(float) +
+         ((size_t)2 * kDeltaBatch * (DPT * LPC + 16 / sizeof(T)) + kDeltaBatch * delta_cols<LPC>()) * sizeof(T);
+}
+
+template <typename T, int DPT, int LPC>
 __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) {
   pdl_wait();
   pdl_trigger();
-  constexpr int Dp = DPT * 4;  // padded key channels
-  __shared__ __align__(16) float sq[kDeltaBatch][Dp];
-  __shared__ __align__(16) float sk[kDeltaBatch][Dp];
-  __shared__ float sv[kDeltaBatch][kDeltaCols];
-  __shared__ float so[kDeltaBatch][kDeltaCols];
-  __shared__ float sbeta[kDeltaBatch], sg[kDeltaBatch];
+  constexpr int Dp = DPT * LPC;  // padded key channels
+  constexpr int RL = delta_row_len<DPT, LPC>();
+  constexpr int E = 16 / (int)sizeof(T);  // elements per 16-byte copy
+  constexpr int RAWL = Dp + E;            // a raw row and its 16 bytes of padding
+  constexpr int kDeltaCols = delta_cols<LPC>();
+  constexpr int CPW = 32 / LPC;           // columns per warp
+  extern __shared__ __align__(16) float sm[];
+  float* sq = sm;                                   // [batch][RL]: channel d of a token at d + 4 (d / DPT)
+  float* sk = sq + kDeltaBatch * RL;
+  float* sv = sk + kDeltaBatch * RL;                // [batch][cols]
+  float* so = sv + kDeltaBatch * kDeltaCols;
+  float* sbeta = so + kDeltaBatch * kDeltaCols;     // [batch]
+  float* sg = sbeta + kDeltaBatch;
+  float* skq = sg + kDeltaBatch;
+  T* qraw = reinterpret_cast<T*>(skq + kDeltaBatch);  // [batch][RAWL]: the next batch as it lies in memory
+  T* kraw = qraw + kDeltaBatch * RAWL;
+  T* vraw = kraw + kDeltaBatch * RAWL;              // [batch][cols]
   const int seg = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
   const int D = a.D, Dv = a.Dv;
   const int q_start = a.seg_info[seg * 4], q_len = a.seg_info[seg * 4 + 1], kv_len = a.seg_info[seg * 4 + 2];
@@ -48,7 +83,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   if (slot < 0 || slot >= a.n_slots) return;
   const int hqk = h / (a.H / a.G);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int slice = lane & 3, lcol = warp * 8 + (lane >> 2), col = col0 + lcol;
+  const int slice = lane % LPC, lcol = warp * CPW + lane / LPC, col = col0 + lcol;
   const int d0 = slice * DPT;
   const bool live = col < Dv;
   float* st = a.state + ((size_t)slot * a.H + h) * D * Dv;
@@ -59,69 +94,126 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   const T* qb = (const T*)a.q; const T* kb = (const T*)a.k; const T* vb = (const T*)a.v;
   const T* bb = (const T*)a.b; const T* ab = (const T*)a.a;
   const float neg_rate = -expf(a.a_log[h]), bias = a.dt_bias[h];
+  const bool wide = a.wide != 0;
+  // the batch from token b0n on, as it lies in memory, into the raw buffers (16 bytes a copy; zeros past the rows' ends)
+  auto fetch = [&](int b0n) {
+    const int nbn = min(kDeltaBatch, q_len - b0n);
+    constexpr int per_row = Dp / E;
+    for (int i = threadIdx.x; i < kDeltaBatch * per_row; i += kDeltaThreads) {
+      const int t = i / per_row, d = (i % per_row) * E;
+      const bool in = t < nbn && d < D;
+      const size_t tok = (size_t)(q_start + b0n + (in ? t : 0));
+      delta_cp16(qraw + t * RAWL + d, in ? qb + tok * a.q_stride + (size_t)hqk * D + d : qb, in);
+      delta_cp16(kraw + t * RAWL + d, in ? kb + tok * a.k_stride + (size_t)hqk * D + d : kb, in);
+    }
+    constexpr int vper = kDeltaCols / E;
+    for (int i = threadIdx.x; i < kDeltaBatch * vper; i += kDeltaThreads) {
+      const int t = i / vper, j = (i % vper) * E;
+      const bool in = t < nbn && col0 + j < Dv;
+      const size_t tok = (size_t)(q_start + b0n + (in ? t : 0));
+      delta_cp16(vraw + t * kDeltaCols + j, in ? vb + tok * a.v_stride + (size_t)h * Dv + col0 + j : vb, in);
+    }
+    delta_cp_commit();
+  };
+  // the gate logits of a batch: a thread a token, fetched a batch ahead into registers
+  float bl_next = 0.f, al_next = 0.f;
+  auto fetch_gates = [&](int b0n) {
+    const int t = threadIdx.x;
+    if (t < kDeltaBatch && b0n + t < q_len) {
+      const size_t tok = (size_t)(q_start + b0n + t);
+      bl_next = to_float(bb[tok * a.b_stride + h]);
+      al_next = to_float(ab[tok * a.a_stride + h]);
+    }
+  };
+  if (wide) fetch(0);
+  fetch_gates(0);
   for (int b0 = 0; b0 < q_len; b0 += kDeltaBatch) {
     const int nb = min(kDeltaBatch, q_len - b0);
-    __syncthreads();  // the batch before is read
-    for (int i = threadIdx.x; i < nb * Dp; i += kDeltaThreads) {
-      const int t = i / Dp, d = i % Dp;
-      const size_t tok = (size_t)(q_start + b0 + t);
-      sq[t][d] = d < D ? to_float(qb[tok * a.q_stride + (size_t)hqk * D + d]) : 0.f;
-      sk[t][d] = d < D ? to_float(kb[tok * a.k_stride + (size_t)hqk * D + d]) : 0.f;
-    }
-    for (int i = threadIdx.x; i < nb * kDeltaCols; i += kDeltaThreads) {
-      const int t = i / kDeltaCols, j = i % kDeltaCols;
-      const size_t tok = (size_t)(q_start + b0 + t);
-      sv[t][j] = col0 + j < Dv ? to_float(vb[tok * a.v_stride + (size_t)h * Dv + col0 + j]) : 0.f;
-    }
+    if (wide) delta_cp_wait_all();
+    __syncthreads();  // the raw rows have landed; the batch before is read and its outputs are written
     if (threadIdx.x < nb) {
-      const size_t tok = (size_t)(q_start + b0 + threadIdx.x);
-      const float bl = to_float(bb[tok * a.b_stride + h]), al = to_float(ab[tok * a.a_stride + h]);
-      sbeta[threadIdx.x] = 1.f / (1.f + expf(-bl));
-      sg[threadIdx.x] = expf(neg_rate * delta_softplus(al + bias));
+      sbeta[threadIdx.x] = 1.f / (1.f + expf(-bl_next));
+      sg[threadIdx.x] = expf(neg_rate * delta_softplus(al_next + bias));
     }
-    __syncthreads();
-    // unit vectors: a warp takes a token at a time
-    for (int t = warp; t < nb; t += kDeltaThreads / 32) {
-      float s2q = 0.f, s2k = 0.f;
-      for (int d = lane; d < Dp; d += 32) { s2q = fmaf(sq[t][d], sq[t][d], s2q); s2k = fmaf(sk[t][d], sk[t][d], s2k); }
-      s2q = warp_sum(s2q); s2k = warp_sum(s2k);
-      const float rq = rsqrtf(s2q + a.unit_eps) * a.q_scale, rk = rsqrtf(s2k + a.unit_eps);
-      for (int d = lane; d < Dp; d += 32) { sq[t][d] *= rq; sk[t][d] *= rk; }
-    }
-    __syncthreads();
-    for (int t = 0; t < nb; ++t) {
-      const float g = sg[t], beta = sbeta[t], vj = sv[t][lcol];
-      const float4* k4 = reinterpret_cast<const float4*>(&sk[t][d0]);
-      const float4* q4 = reinterpret_cast<const float4*>(&sq[t][d0]);
-      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
-#pragma unroll
-      for (int i = 0; i < DPT / 4; ++i) {
-        const float4 kv = k4[i];
-        r0 = fmaf(s[4 * i + 0], kv.x, r0); r1 = fmaf(s[4 * i + 1], kv.y, r1);
-        r2 = fmaf(s[4 * i + 2], kv.z, r2); r3 = fmaf(s[4 * i + 3], kv.w, r3);
+    if (!wide) {  // rows that do not allow 16-byte copies: element by element, straight from memory
+      for (int i = threadIdx.x; i < kDeltaBatch * Dp; i += kDeltaThreads) {
+        const int t = i / Dp, d = i % Dp;
+        const bool in = t < nb && d < D;
+        const size_t tok = (size_t)(q_start + b0 + (in ? t : 0));
+        qraw[t * RAWL + d] = in ? qb[tok * a.q_stride + (size_t)hqk * D + d] : from_float<T>(0.f);
+        kraw[t * RAWL + d] = in ? kb[tok * a.k_stride + (size_t)hqk * D + d] : from_float<T>(0.f);
       }
-      float r = (r0 + r1) + (r2 + r3);
-      r += __shfl_xor_sync(0xffffffffu, r, 1);
-      r += __shfl_xor_sync(0xffffffffu, r, 2);
-      const float u = beta * (vj - g * r);  // S^T k of the decayed state is g times that of the state as found
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      for (int i = threadIdx.x; i < kDeltaBatch * kDeltaCols; i += kDeltaThreads) {
+        const int t = i / kDeltaCols, j = i % kDeltaCols;
+        const bool in = t < nb && col0 + j < Dv;
+        const size_t tok = (size_t)(q_start + b0 + (in ? t : 0));
+        vraw[i] = in ? vb[tok * a.v_stride + (size_t)h * Dv + col0 + j] : from_float<T>(0.f);
+      }
+      __syncthreads();
+    }
+    // widen; unit vectors and k . q: eight lanes a token, a warp four tokens at a time
+    for (int t = warp * 4 + (lane >> 3); t < kDeltaBatch; t += kDeltaThreads / 8) {
+      const int sub = lane & 7;
+      float s2q = 0.f, s2k = 0.f, dkq = 0.f;
+      for (int d = sub; d < Dp; d += 8) {
+        const float qv = to_float(qraw[t * RAWL + d]), kv = to_float(kraw[t * RAWL + d]);
+        s2q = fmaf(qv, qv, s2q); s2k = fmaf(kv, kv, s2k); dkq = fmaf(qv, kv, dkq);
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) {
+        s2q += __shfl_xor_sync(0xffffffffu, s2q, o);
+        s2k += __shfl_xor_sync(0xffffffffu, s2k, o);
+        dkq += __shfl_xor_sync(0xffffffffu, dkq, o);
+      }
+      const float rq = rsqrtf(s2q + a.unit_eps) * a.q_scale, rk = rsqrtf(s2k + a.unit_eps);
+      for (int d = sub; d < Dp; d += 8) {
+        const int at = t * RL + d + 4 * (d / DPT);
+        sq[at] = to_float(qraw[t * RAWL + d]) * rq;
+        sk[at] = to_float(kraw[t * RAWL + d]) * rk;
+      }
+      if (sub == 0) skq[t] = dkq * rq * rk;
+    }
+    for (int i = threadIdx.x; i < kDeltaBatch * kDeltaCols; i += kDeltaThreads) sv[i] = to_float(vraw[i]);
+    __syncthreads();  // the raw buffers are read: the next batch may land
+    if (b0 + kDeltaBatch < q_len) {
+      if (wide) fetch(b0 + kDeltaBatch);
+      fetch_gates(b0 + kDeltaBatch);
+    }
+    for (int t = 0; t < nb; ++t) {
+      const float g = sg[t], beta = sbeta[t], kq = skq[t], vj = sv[t * kDeltaCols + lcol];
+      const float4* k4 = reinterpret_cast<const float4*>(sk + t * RL + d0 + 4 * slice);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + t * RL + d0 + 4 * slice);
+      float4 kr[DPT / 4];
+      float r[4] = {0.f, 0.f, 0.f, 0.f}, pp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DPT / 4; ++i) {
         const float4 kv = k4[i], qv = q4[i];
-        s[4 * i + 0] = fmaf(g, s[4 * i + 0], kv.x * u); o0 = fmaf(s[4 * i + 0], qv.x, o0);
-        s[4 * i + 1] = fmaf(g, s[4 * i + 1], kv.y * u); o1 = fmaf(s[4 * i + 1], qv.y, o1);
-        s[4 * i + 2] = fmaf(g, s[4 * i + 2], kv.z * u); o2 = fmaf(s[4 * i + 2], qv.z, o2);
-        s[4 * i + 3] = fmaf(g, s[4 * i + 3], kv.w * u); o3 = fmaf(s[4 * i + 3], qv.w, o3);
+        kr[i] = kv;
+        r[0] = fmaf(s[4 * i + 0], kv.x, r[0]); pp[0] = fmaf(s[4 * i + 0], qv.x, pp[0]);
+        r[1] = fmaf(s[4 * i + 1], kv.y, r[1]); pp[1] = fmaf(s[4 * i + 1], qv.y, pp[1]);
+        r[2] = fmaf(s[4 * i + 2], kv.z, r[2]); pp[2] = fmaf(s[4 * i + 2], qv.z, pp[2]);
+        r[3] = fmaf(s[4 * i + 3], kv.w, r[3]); pp[3] = fmaf(s[4 * i + 3], qv.w, pp[3]);
       }
-      float o = (o0 + o1) + (o2 + o3);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (slice == 0) so[t][lcol] = o;
+      float rs = (r[0] + r[1]) + (r[2] + r[3]), ps = (pp[0] + pp[1]) + (pp[2] + pp[3]);
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) {
+        rs += __shfl_xor_sync(0xffffffffu, rs, o);
+        ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      }
+      const float u = beta * (vj - g * rs);  // S^T k of the decayed state is g times that of the state as found
+#pragma unroll
+      for (int i = 0; i < DPT / 4; ++i) {
+        s[4 * i + 0] = fmaf(g, s[4 * i + 0], kr[i].x * u);
+        s[4 * i + 1] = fmaf(g, s[4 * i + 1], kr[i].y * u);
+        s[4 * i + 2] = fmaf(g, s[4 * i + 2], kr[i].z * u);
+        s[4 * i + 3] = fmaf(g, s[4 * i + 3], kr[i].w * u);
+      }
+      if (slice == 0) so[t * kDeltaCols + lcol] = fmaf(g, ps, kq * u);  // S_new^T q = g S^T q + (k . q) u
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nb * kDeltaCols; i += kDeltaThreads) {
       const int t = i / kDeltaCols, j = i % kDeltaCols;
-      if (col0 + j < Dv) a.out[((size_t)(q_start + b0 + t) * a.H + h) * Dv + col0 + j] = so[t][j];
+      if (col0 + j < Dv) a.out[((size_t)(q_start + b0 + t) * a.H + h) * Dv + col0 + j] = so[i];
     }
   }
   if (live) {
@@ -131,16 +223,28 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   }
 }
 
-template <typename T>
-static int launch_delta(const DeltaArgs& a, cudaStream_t s) {
+template <typename T, int DPT, int LPC>
+static int launch_delta_sized(const DeltaArgs& a, cudaStream_t s) {
+  constexpr int kDeltaCols = delta_cols<LPC>();
   dim3 grid(a.n_segs, a.H, (a.Dv + kDeltaCols - 1) / kDeltaCols);
-  if (a.D <= 16) FTK_LAUNCH((delta_scan_kernel<T, 4>), grid, kDeltaThreads, 0, s, a);
-  else if (a.D <= 32) FTK_LAUNCH((delta_scan_kernel<T, 8>), grid, kDeltaThreads, 0, s, a);
-  else if (a.D <= 64) FTK_LAUNCH((delta_scan_kernel<T, 16>), grid, kDeltaThreads, 0, s, a);
-  else if (a.D <= 128) FTK_LAUNCH((delta_scan_kernel<T, 32>), grid, kDeltaThreads, 0, s, a);
-  else FTK_LAUNCH((delta_scan_kernel<T, 64>), grid, kDeltaThreads, 0, s, a);
+  constexpr size_t smem = delta_smem_bytes<T, DPT, LPC>();
+  auto kern = delta_scan_kernel<T, DPT, LPC>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  FTK_LAUNCH(kern, grid, kDeltaThreads, smem, s, a);
   FTK_LAUNCH_CHECK("delta_scan");
   return 0;
+}
+
+template <typename T>
+static int launch_delta(DeltaArgs a, cudaStream_t s) {
+  const long long e = 16 / (long long)sizeof(T);
+  a.wide = a.D % e == 0 && a.Dv % e == 0 && a.q_stride % e == 0 && a.k_stride % e == 0 && a.v_stride % e == 0 &&
+           (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v) & 15) == 0;
+  if (a.D <= 16) return launch_delta_sized<T, 4, 4>(a, s);
+  if (a.D <= 32) return launch_delta_sized<T, 4, 8>(a, s);
+  if (a.D <= 64) return launch_delta_sized<T, 8, 8>(a, s);
+  if (a.D <= 128) return launch_delta_sized<T, 16, 8>(a, s);
+  return launch_delta_sized<T, 32, 8>(a, s);
 }
 
 }  // namespace ftk
@@ -156,7 +260,7 @@ extern "C" int ftk_delta_scan(const void* q, long long q_stride, const void* k, 
   FTK_REQUIRE(n_tokens >= 0 && n_segs >= 0, "delta_scan: bad counts");
   if (n_tokens == 0 || n_segs == 0) return 0;
   FTK_REQUIRE(n_heads >= 1 && n_heads <= 65535 && n_kv_heads >= 1 && n_heads % n_kv_heads == 0 && dim >= 1 && dim <= 256 &&
-              vdim >= 1 && vdim <= 65535 * kDeltaCols,
+              vdim >= 1 && vdim <= 65535 * 16 && (long long)n_heads <= 65535,
               "delta_scan: %d heads on %d key heads of %d key and %d value channels are not taken (at most 256 key channels)",
               n_heads, n_kv_heads, dim, vdim);
   FTK_REQUIRE(q && k && v && b && a && a_log && dt_bias && state && state_slots && seg_info && out, "delta_scan: null pointer");
