@@ -163,7 +163,7 @@ int ftk_ssm_output(const float* o32, const void* x, long long x_stride, const fl
 // Gated delta rule (delta.cu): per (segment, head) and token in order, S <- g S; u = beta (v - S^T k); S <- S + k u^T;
 // o = S^T q, with beta = sigmoid(b), g = exp(-exp(a_log) softplus(a + dt_bias)), q and k made unit vectors per head
 // (x / sqrt(sum x^2 + unit_eps), q then times q_scale).  q, k hold n_kv_heads heads of `dim`; state [n_slots, n_heads,
-// dim, vdim] float32; out [T, n_heads, vdim] float32.
+// vdim, dim] float32 (column by column); out [T, n_heads, vdim] float32.
 int ftk_delta_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
                    const void* b, long long b_stride, const void* a, long long a_stride, int dtype, const float* a_log,
                    const float* dt_bias, float q_scale, float unit_eps, float* state, int n_slots,

@@ -2,7 +2,8 @@
 // value along its key, then reads with its query:
 //   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q.
 // beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)); q and k are made unit vectors per head first
-// (x / sqrt(sum x^2 + eps)), q also scaled.  State, gates, norms and all sums are 32-bit.
+// (x / sqrt(sum x^2 + eps)), q also scaled.  State, gates, norms and all sums are 32-bit.  The state is kept
+// column by column, [value column][key channel], so that a thread's share of a column is one stretch of memory.
 //
 // The correction u needs S^T k of the state as the token finds it, so a request's tokens run one after the other.
 // What runs side by side are the state's columns: a block owns 16 value columns of one (request, head); eight
@@ -86,11 +87,21 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   const int slice = lane % LPC, lcol = warp * CPW + lane / LPC, col = col0 + lcol;
   const int d0 = slice * DPT;
   const bool live = col < Dv;
-  float* st = a.state + ((size_t)slot * a.H + h) * D * Dv;
+  // the state lies column by column ([Dv][D]): a thread's channels of its column are neighbours in memory
+  float* st = a.state + (((size_t)slot * a.H + h) * Dv + (live ? col : 0)) * D + d0;
   const bool fresh = kv_len == q_len;
+  const bool quads = (D & 3) == 0;  // (the state's rows then start on 16 bytes: float4 accesses)
   float s[DPT];
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) s[i] = (!fresh && live && d0 + i < D) ? st[(size_t)(d0 + i) * Dv + col] : 0.f;
+  for (int i = 0; i < DPT; i += 4) {
+    if (!fresh && live && quads && d0 + i + 4 <= D) {
+      const float4 f = *reinterpret_cast<const float4*>(st + i);
+      s[i] = f.x; s[i + 1] = f.y; s[i + 2] = f.z; s[i + 3] = f.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[i + e] = (!fresh && live && d0 + i + e < D) ? st[i + e] : 0.f;
+    }
+  }
   const T* qb = (const T*)a.q; const T* kb = (const T*)a.k; const T* vb = (const T*)a.v;
   const T* bb = (const T*)a.b; const T* ab = (const T*)a.a;
   const float neg_rate = -expf(a.a_log[h]), bias = a.dt_bias[h];
@@ -218,8 +229,15 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DPT; ++i)
-      if (d0 + i < D) st[(size_t)(d0 + i) * Dv + col] = s[i];
+    for (int i = 0; i < DPT; i += 4) {
+      if (quads && d0 + i + 4 <= D) {
+        *reinterpret_cast<float4*>(st + i) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (d0 + i + e < D) st[i + e] = s[i + e];
+      }
+    }
   }
 }
 

@@ -477,7 +477,7 @@ def bench_nusudra(a) -> dict:
     qkv = torch.empty(T, dconv, dtype=bf, device=dev)
     add("conv_act (no bias, silu: q, k, v of the delta rule)",
         lambda: ops.conv_act(dproj[:, :dconv], dw, None, "silu", dstate_c, slots, seg, len(segs), qkv), T * dconv * 4)
-    dstate = torch.zeros(n_slots, H, D, Dv, device=dev)
+    dstate = torch.zeros(n_slots, H, Dv, D, device=dev)
     do32 = torch.empty(T, H, Dv, device=dev)
     al, db = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
     add("delta_scan",

@@ -1393,12 +1393,12 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_raw: torch.T
     (``x / sqrt(sum(x^2) + unit_eps)``; ``q`` then times ``q_scale``).
 
     ``q, k [T, G * D]``, ``v [T, H * Dv]``, ``b_raw, a_raw [T, H]`` of the engine's dtype (views of adjacent columns
-    are fine; head ``h`` reads q/k head ``h // (H / G)``); ``a_log, dt_bias [H]`` float32; ``state [slots, H, D, Dv]``
-    float32, read from and left in the slot ``state_slots[segment]`` (a segment with ``kv_len == q_len`` starts from
+    are fine; head ``h`` reads q/k head ``h // (H / G)``); ``a_log, dt_bias [H]`` float32; ``state [slots, H, Dv, D]``
+    float32 (``S`` column by column: a value column's key channels are neighbours), read from and left in the slot ``state_slots[segment]`` (a segment with ``kv_len == q_len`` starts from
     zero); ``out [T, H, Dv]`` float32.  Everything but the reading of the rows is 32-bit."""
     T, H, Dv = out.shape
-    D = state.shape[2]
-    if state.shape[1] != H or state.shape[3] != Dv or q.shape[1] % D or H % (q.shape[1] // D) or D > 256:
+    D = state.shape[3]
+    if state.shape[1] != H or state.shape[2] != Dv or q.shape[1] % D or H % (q.shape[1] // D) or D > 256:
         raise KernelError("delta_scan: shapes do not agree (keys of at most 256 channels)")
     G = q.shape[1] // D
     qs, ks = _cols(q, "delta_scan: q", (T, G * D)), _cols(k, "delta_scan: k", (T, G * D), q.dtype)

@@ -15,7 +15,7 @@ one plain weight ``[v_head_dim]`` for all heads and by ``silu`` of the gate, and
 Unit norms, ``beta``, ``g``, the state and all of the recurrence's sums are 32-bit (:func:`ops.delta_scan`, which
 takes the logits and the convolved rows as they lie and runs a request's tokens in order, the state's columns
 spread over threads); the output norm and gate are :func:`ops.gated_heads`.  Per request the layer keeps the state
-``[n_heads, head_dim, v_head_dim]`` and the convolution's last ``taps - 1`` inputs in one slot of the cache manager's
+``S`` (stored column by column, ``[n_heads, v_head_dim, head_dim]``) and the convolution's last ``taps - 1`` inputs in one slot of the cache manager's
 state pool; both start from zero.  The reference has no recurrent mixer.
 """
 
@@ -79,7 +79,7 @@ class GatedDelta(Mixer):
         }
 
     def cache_need(self):
-        tensors = [("s", (self.n_heads, self.head_dim, self.v_dim), "float32")]
+        tensors = [("s", (self.n_heads, self.v_dim, self.head_dim), "float32")]  # S column by column
         if self.taps > 1:
             tensors.append(("conv", (self.taps - 1, self.conv_dim), "float32"))
         return StateNeed(tuple(tensors))

@@ -614,7 +614,7 @@ def ssm_output(o32, x, d_skip, z, norm_weight, norm_groups, eps, out):
 
 def delta_scan(q, k, v, b_raw, a_raw, a_log, dt_bias, q_scale, unit_eps, state, state_slots, seg_info, n_segs, out):
     T, H, Dv = out.shape
-    D = state.shape[2]
+    D = state.shape[3]  # the state is kept column by column: [slots, H, Dv, D]
     G = q.shape[1] // D
     qq, kk = q.float().view(T, G, D), k.float().view(T, G, D)
     qq = qq * torch.rsqrt((qq * qq).sum(-1, keepdim=True) + unit_eps) * q_scale
@@ -625,13 +625,13 @@ def delta_scan(q, k, v, b_raw, a_raw, a_log, dt_bias, q_scale, unit_eps, state, 
     g = torch.exp(-torch.exp(a_log.float()) * torch.nn.functional.softplus(a_raw.float() + dt_bias.float(), threshold=1e9))
     for i, (q_start, q_len, kv_len, _) in enumerate(seg_info.view(-1, 4)[:n_segs].tolist()):
         slot = int(state_slots[i])
-        S = torch.zeros(H, D, Dv) if kv_len == q_len else state[slot].clone()
+        S = torch.zeros(H, D, Dv) if kv_len == q_len else state[slot].transpose(1, 2).clone()
         for t in range(q_start, q_start + q_len):
             S = g[t][:, None, None] * S
             u = beta[t][:, None] * (vv[t] - torch.einsum("hdv,hd->hv", S, kk[t]))
             S = S + kk[t][:, :, None] * u[:, None, :]
             out[t] = torch.einsum("hdv,hd->hv", S, qq[t])
-        state[slot] = S
+        state[slot] = S.transpose(1, 2)
 
 
 ALL = ["hyper_step", "norm_mean", "conv_act", "ssm_gates", "ssm_output", "delta_scan", "short_conv", "depth_mix", "moe_gather_scaled", "relu2_", "latent_store", "latent_query_rotate", "mlstm_gates", "mlstm_output", "linear_f32", "softcap_", "postnorm_add_norm", "gated_heads", "gla_scan", "stream_add_norm", "head_gate", "table_route", "scale_", "sparse_score_fits", "moe_small_fits", "copy_tokens", "sparse_select", "embedding_gather", "add_rmsnorm", "add_rmsnorm_routes", "act_and_mul", "cast", "table_update", "norm_rope_store",

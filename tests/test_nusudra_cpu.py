@@ -103,7 +103,7 @@ def test_pages_and_states():
     cpu = torch.device("cpu")
     model = Model(spec, BuildEnv(dtype=torch.float32, device=cpu, max_seq_len=8, max_step_tokens=8, workspace=Workspace(cpu)))
     needs = dict(model.cache_needs())
-    assert needs[0] == StateNeed((("s", (4, 16, 24), "float32"), ("conv", (2, 2 * 16 + 2 * 16 + 4 * 24), "float32")))
+    assert needs[0] == StateNeed((("s", (4, 24, 16), "float32"), ("conv", (2, 2 * 16 + 2 * 16 + 4 * 24), "float32")))
     assert needs[(1, 0)] == PagedKVNeed((("k", 2, 32), ("v", 2, 32)), None)  # keys of 16 and values of 24 on rows of 32
     assert needs[(1, 1)] == StateNeed((("s", (4, 16, 8), "float32"), ("conv", (1, 32 + 2 * 32), "float32")))
     assert needs[2] == PagedKVNeed((("kv", 1, 32),), None)  # one row of latent and rotated part per token, padded to 16s
@@ -111,7 +111,7 @@ def test_pages_and_states():
     assert len(blocks) == 4 and blocks[0] == StateNeed((("shift", (1, 64), "float32"),))
     _, _, spec2, _ = describe_model(NUSU_2)
     model2 = Model(spec2, BuildEnv(dtype=torch.float32, device=cpu, max_seq_len=8, max_step_tokens=8, workspace=Workspace(cpu)))
-    assert dict(model2.cache_needs())[1] == StateNeed((("s", (1, 22, 14), "float32"),))  # one tap: no convolution state
+    assert dict(model2.cache_needs())[1] == StateNeed((("s", (1, 14, 22), "float32"),))  # one tap: no convolution state
 
 
 # --------------------------------------------------------------------------- the plain mechanisms among themselves

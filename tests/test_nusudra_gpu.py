@@ -210,7 +210,7 @@ def test_delta_rule_against_the_stated_recurrence(dtype, H, G, D, Dv):
     v = rows[:, 2 * G * D:2 * G * D + H * Dv]
     b, a = rows[:, -2 * H - 3:-H - 3], rows[:, -H - 3:-3]
     a_log, dt_bias = rnd(H, seed=2, scale=0.5) - 1.0, rnd(H, seed=3)
-    state = rnd(len(lens) + 1, H, D, Dv, seed=4, scale=0.3)
+    state = rnd(len(lens) + 1, H, Dv, D, seed=4, scale=0.3)
     st_a, st_b = state.clone(), state.cpu().clone()
     got, want = torch.zeros(T, H, Dv, device=DEV), torch.zeros(T, H, Dv)
     ops.delta_scan(q, k, v, b, a, a_log, dt_bias, D ** -0.5, 1e-6, st_a, slots, info, len(lens), got)
@@ -244,7 +244,7 @@ def test_a_value_written_once_is_read_hundreds_of_tokens_later(cuts):
     a = torch.full((T, H), -9.0)  # softplus near zero: decays near one
     a_log, dt_bias = torch.zeros(H), torch.zeros(H)
     dev = lambda t: t.to(DEV).contiguous()  # noqa: E731
-    state = torch.full((2, H, D, Dv), 3.0, device=DEV)
+    state = torch.full((2, H, Dv, D), 3.0, device=DEV)
     outs, i = [], 0
     for c in cuts:
         info, slots, _ = segs([(c, i + c)])
@@ -256,7 +256,7 @@ def test_a_value_written_once_is_read_hundreds_of_tokens_later(cuts):
     got = torch.cat(outs).cpu()
     want = torch.zeros(T, H, Dv)
     info, slots, _ = segs([(T, T)])
-    ref.delta_scan(q, k, v, b, a, a_log, dt_bias, 1.0, 1e-6, torch.zeros(2, H, D, Dv), slots.cpu(), info.cpu(), 1, want)
+    ref.delta_scan(q, k, v, b, a, a_log, dt_bias, 1.0, 1e-6, torch.zeros(2, H, Dv, D), slots.cpu(), info.cpu(), 1, want)
     torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
     read = got[T - 1].reshape(-1)
     kept = float(torch.sigmoid(torch.tensor(4.0))) * float(torch.exp(-torch.nn.functional.softplus(torch.tensor(-9.0)))) ** (T - 4)
