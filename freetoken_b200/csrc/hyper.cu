@@ -22,7 +22,9 @@ struct HyperArgs {
   float eps; void* h_out; float* sum_out;
 };
 
-template <typename TY, typename TH>
+// MAXS: the smallest of 1, 2, 4, 8 that holds the streams (a token's streams stay in registers: the fewer the kernel
+// sets aside, the more blocks an SM holds)
+template <typename TY, typename TH, int MAXS>
 __global__ void __launch_bounds__(kHyperThreads) hyper_step_kernel(HyperArgs a) {
   pdl_wait();
   pdl_trigger();
@@ -43,74 +45,61 @@ __global__ void __launch_bounds__(kHyperThreads) hyper_step_kernel(HyperArgs a) 
   float ss = 0.f;
   for (int c0 = threadIdx.x * 4; c0 < C; c0 += blockDim.x * 4) {
     const int nc = min(4, C - c0);
-    float x[kHyperMaxStreams][4];
+    float x[MAXS][4];
     if (init) {
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (vec) Vec4<float>::load(init + c0, v);
       else for (int i = 0; i < nc; ++i) v[i] = init[c0 + i];
 #pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
-        if (s < S)
+      for (int s = 0; s < MAXS; ++s)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) x[s][i] = v[i];
+        for (int i = 0; i < 4; ++i) x[s][i] = v[i];
     } else {
 #pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
+      for (int s = 0; s < MAXS; ++s)
         if (s < S) {
           const float* src = a.streams + (size_t)s * a.stream_stride + t * C + c0;
           if (vec) Vec4<float>::load(src, x[s]);
           else for (int i = 0; i < 4; ++i) x[s][i] = i < nc ? src[i] : 0.f;
         }
     }
+    float yv[4] = {0.f, 0.f, 0.f, 0.f};
     if (y) {
-      float yv[4] = {0.f, 0.f, 0.f, 0.f};
       if (vec) Vec4<TY>::load(y + c0, yv);
       else for (int i = 0; i < nc; ++i) yv[i] = to_float(y[c0 + i]);
-      float nx[kHyperMaxStreams][4];
+    }
+    // one new stream after the other, each from all the old ones: stored, and added to what is read from the new streams
+    float u[4] = {0.f, 0.f, 0.f, 0.f}, z[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int to = 0; to < kHyperMaxStreams; ++to)
-        if (to < S) {
+    for (int to = 0; to < MAXS; ++to)
+      if (to < S) {
+        float v[4];
+        if (y) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) nx[to][i] = 0.f;
+          for (int i = 0; i < 4; ++i) v[i] = 0.f;
 #pragma unroll
-          for (int s = 0; s < kHyperMaxStreams; ++s)
+          for (int s = 0; s < MAXS; ++s)
             if (s < S)
 #pragma unroll
-              for (int i = 0; i < 4; ++i) nx[to][i] = fmaf(cmix[s * S + to], x[s][i], nx[to][i]);
+              for (int i = 0; i < 4; ++i) v[i] = fmaf(cmix[s * S + to], x[s][i], v[i]);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) nx[to][i] = fmaf(cout[to], yv[i], nx[to][i]);
+          for (int i = 0; i < 4; ++i) v[i] = fmaf(cout[to], yv[i], v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[i] = x[to][i];
+        }
+        if (writes) {
+          float* dst = a.streams + (size_t)to * a.stream_stride + t * C + c0;
+          if (vec) Vec4<float>::store(dst, v);
+          else for (int i = 0; i < nc; ++i) dst[i] = v[i];
         }
 #pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
-        if (s < S)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) x[s][i] = nx[s][i];
-    }
-    if (writes) {
-#pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
-        if (s < S) {
-          float* dst = a.streams + (size_t)s * a.stream_stride + t * C + c0;
-          if (vec) Vec4<float>::store(dst, x[s]);
-          else for (int i = 0; i < nc; ++i) dst[i] = x[s][i];
-        }
-    }
+        for (int i = 0; i < 4; ++i) { u[i] = fmaf(cin[to], v[i], u[i]); z[i] += v[i]; }
+      }
     if (a.in_w) {
-      float u[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
-        if (s < S)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) u[i] = fmaf(cin[s], x[s][i], u[i]);
       for (int i = 0; i < nc; ++i) { u_row[c0 + i] = u[i]; ss = fmaf(u[i], u[i], ss); }
     }
     if (a.sum_out) {
-      float z[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s)
-        if (s < S)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) z[i] += x[s][i];
       float* dst = a.sum_out + t * C + c0;
       if (vec) Vec4<float>::store(dst, z);
       else for (int i = 0; i < nc; ++i) dst[i] = z[i];
@@ -199,17 +188,25 @@ extern "C" int ftk_hyper_step(float* streams, long long stream_stride, int n_str
   const size_t smem = ((size_t)((channels + 3) & ~3) + 33) * sizeof(float);
   FTK_REQUIRE(smem <= 200 * 1024, "hyper_step: rows of %d channels do not fit shared memory", channels);
   cudaStream_t s = (cudaStream_t)stream;
-#define FTK_HYPER(TY, TH)                                                                          \
+#define FTK_HYPER_N(TY, TH, N)                                                                     \
   do {                                                                                             \
-    auto kern = hyper_step_kernel<TY, TH>;                                                         \
+    auto kern = hyper_step_kernel<TY, TH, N>;                                                      \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     FTK_LAUNCH(kern, n_tokens, kHyperThreads, smem, s, a);                                         \
+  } while (0)
+#define FTK_HYPER(TY, TH)                          \
+  do {                                             \
+    if (n_streams == 1) FTK_HYPER_N(TY, TH, 1);    \
+    else if (n_streams == 2) FTK_HYPER_N(TY, TH, 2); \
+    else if (n_streams <= 4) FTK_HYPER_N(TY, TH, 4); \
+    else FTK_HYPER_N(TY, TH, 8);                   \
   } while (0)
   if (y_dtype == FTK_F32 && h_dtype == FTK_F32) FTK_HYPER(float, float);
   else if (y_dtype == FTK_F32) FTK_HYPER(float, __nv_bfloat16);
   else if (h_dtype == FTK_F32) FTK_HYPER(__nv_bfloat16, float);
   else FTK_HYPER(__nv_bfloat16, __nv_bfloat16);
 #undef FTK_HYPER
+#undef FTK_HYPER_N
   FTK_LAUNCH_CHECK("hyper_step");
   return 0;
 }
