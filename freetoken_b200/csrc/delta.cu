@@ -6,11 +6,10 @@
 // column by column, [value column][key channel], so that a thread's share of a column is one stretch of memory.
 //
 // The correction u needs S^T k of the state as the token finds it, so a request's tokens run one after the other.
-// What runs side by side are the state's columns: a block owns 16 value columns of one (request, head); eight
-// neighbouring lanes share a column, each keeping an eighth of its key channels in registers (the kernel is bound
-// by the latency of a token's chain of sums, shuffles and updates, so many short chains in many warps beat few
-// long ones).  One pass over a thread's share of the state gives both S^T k and S^T q of the state as found (three
-// shuffles each, interleaved), and the token's output follows without a second pass: with r = S^T k, p = S^T q of
+// What runs side by side are the state's columns: a block owns 16 to 64 value columns of one (request, head); eight
+// (or four, or two) neighbouring lanes share a column, each keeping its share of the column's key channels in
+// registers.  One pass over a thread's share of the state gives both S^T k and S^T q of the state as found (a few
+// shuffle rounds, interleaved), and the token's output follows without a second pass: with r = S^T k, p = S^T q of
 // the state before the decay,
 //   u = beta (v - g r),   o = g p + (k . q) u,   S <- g S + k u^T.
 // The tokens' q, k, v come through shared memory 16 tokens at a time: rows that allow 16-byte copies are fetched a
@@ -51,7 +50,7 @@ template <int LPC>
 __host__ __device__ constexpr int delta_cols() { return kDeltaThreads / LPC; }  // value columns per block
 template <typename T, int DPT, int LPC>
 __host__ __device__ constexpr size_t delta_smem_bytes() {
-  return ((size_t)2 * kDeltaBatch * delta_row_len<DPT, LPC>() + 2 * kDeltaBatch * delta_cols<LPC>() + 3 * kDeltaBatch) * sizeof(float) +
+  return ((size_t)2 * kDeltaBatch * delta_row_len<DPT, LPC>() + kDeltaBatch * delta_cols<LPC>() + 3 * kDeltaBatch) * sizeof(float) +
          ((size_t)2 * kDeltaBatch * (DPT * LPC + 16 / sizeof(T)) + kDeltaBatch * delta_cols<LPC>()) * sizeof(T);
 }
 
@@ -69,8 +68,9 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   float* sq = sm;                                   // [batch][RL]: channel d of a token at d + 4 (d / DPT)
   float* sk = sq + kDeltaBatch * RL;
   float* sv = sk + kDeltaBatch * RL;                // [batch][cols]
-  float* so = sv + kDeltaBatch * kDeltaCols;
-  float* sbeta = so + kDeltaBatch * kDeltaCols;     // [batch]
+  // (the outputs of a batch lie in an array of their own: the token loop's loads may then pass its stores)
+  __shared__ float so[kDeltaBatch * kDeltaCols];
+  float* sbeta = sv + kDeltaBatch * kDeltaCols;     // [batch]
   float* sg = sbeta + kDeltaBatch;
   float* skq = sg + kDeltaBatch;
   T* qraw = reinterpret_cast<T*>(skq + kDeltaBatch);  // [batch][RAWL]: the next batch as it lies in memory
@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
       if (wide) fetch(b0 + kDeltaBatch);
       fetch_gates(b0 + kDeltaBatch);
     }
+#pragma unroll 4
     for (int t = 0; t < nb; ++t) {
       const float g = sg[t], beta = sbeta[t], kq = skq[t], vj = sv[t * kDeltaCols + lcol];
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * RL + d0 + 4 * slice);
@@ -261,7 +262,12 @@ static int launch_delta(DeltaArgs a, cudaStream_t s) {
   if (a.D <= 16) return launch_delta_sized<T, 4, 4>(a, s);
   if (a.D <= 32) return launch_delta_sized<T, 4, 8>(a, s);
   if (a.D <= 64) return launch_delta_sized<T, 8, 8>(a, s);
-  if (a.D <= 128) return launch_delta_sized<T, 16, 8>(a, s);
+  if (a.D <= 128) {
+    // two lanes a column (64 channels a thread, one shuffle round) once the step has columns enough for every SM that way;
+    // measured on B200, 48 heads of 128 x 128, 2,048 tokens: 856 us against 988 (four lanes) and 910 (eight)
+    if ((long long)a.n_segs * a.H * a.Dv >= 148 * 32) return launch_delta_sized<T, 64, 2>(a, s);
+    return launch_delta_sized<T, 16, 8>(a, s);
+  }
   return launch_delta_sized<T, 32, 8>(a, s);
 }
 
