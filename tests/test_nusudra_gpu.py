@@ -201,7 +201,8 @@ def test_the_recurrence_with_queries_and_keys_shared_by_groups_of_heads(dtype, H
 # --------------------------------------------------------------------------- delta rule
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,Dv", [(4, 4, 32, 64), (4, 2, 16, 24), (3, 1, 40, 10), (2, 2, 8, 33), (1, 1, 128, 128),
-                                      (2, 1, 200, 70), (6, 3, 6, 5)])
+                                      (2, 1, 200, 70), (6, 3, 6, 5), (8, 2, 128, 128), (8, 4, 96, 104)])  # (the last two: the form
+# with two lanes a column, which steps with thousands of columns take)
 def test_delta_rule_against_the_stated_recurrence(dtype, H, G, D, Dv):
     lens = [(45, 45), (1, 40), (17, 100), (2, 2), (1, 1), (33, 64)]
     info, slots, T = segs(lens)
