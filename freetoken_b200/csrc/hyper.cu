@@ -118,13 +118,17 @@ __global__ void __launch_bounds__(kHyperThreads) hyper_step_kernel(HyperArgs a) 
   }
 }
 
-struct NormMeanArgs { const void* xs[4]; const float* ws[4]; int n, C; float eps; void* out; };
+struct NormMeanArgs { const void* xs[4]; const float* ws[4]; int n, C; float eps; void* out; int keep; };
 
+// keep: the rows stay in shared memory between the pass that takes their mean squares and the pass that adds them up
+// (n * C values of T behind the scratch); otherwise the second pass reads them again
 template <typename T>
 __global__ void __launch_bounds__(kHyperThreads) norm_mean_kernel(NormMeanArgs a) {
   pdl_wait();
   pdl_trigger();
-  __shared__ float scratch[33];
+  extern __shared__ __align__(16) float nm_sm[];
+  float* scratch = nm_sm;  // 33 floats (36 set aside)
+  T* kept = reinterpret_cast<T*>(nm_sm + 36);
   const size_t t = blockIdx.x;
   const int C = a.C;
   const bool vec = (C & 3) == 0;
@@ -140,6 +144,10 @@ __global__ void __launch_bounds__(kHyperThreads) norm_mean_kernel(NormMeanArgs a
       if (vec) Vec4<T>::load(x + c0, v);
       else for (int i = 0; i < nc; ++i) v[i] = to_float(x[c0 + i]);
       for (int i = 0; i < 4; ++i) ss = fmaf(v[i], v[i], ss);
+      if (a.keep) {
+        if (vec) Vec4<T>::store(kept + (size_t)j * C + c0, v);
+        else for (int i = 0; i < nc; ++i) kept[(size_t)j * C + c0 + i] = from_float<T>(v[i]);
+      }
     }
     ss = block_sum(ss, scratch);
     r[j] = rsqrtf(ss / (float)C + a.eps);
@@ -152,7 +160,7 @@ __global__ void __launch_bounds__(kHyperThreads) norm_mean_kernel(NormMeanArgs a
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (j >= a.n) break;
-      const T* x = (const T*)a.xs[j] + t * C;
+      const T* x = a.keep ? kept + (size_t)j * C : (const T*)a.xs[j] + t * C;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (vec) Vec4<T>::load(x + c0, v);
       else for (int i = 0; i < nc; ++i) v[i] = to_float(x[c0 + i]);
@@ -227,9 +235,12 @@ extern "C" int ftk_norm_mean(const void* const* xs, const float* const* ws, int 
   }
   FTK_REQUIRE((bits & 15) == 0, "norm_mean: 16-byte aligned rows only");
   a.n = n; a.C = channels; a.eps = eps; a.out = out;
+  const size_t rows = (size_t)n * channels * dtype_size(dtype);
+  a.keep = rows <= 40 * 1024 && channels % 4 == 0 ? 1 : 0;  // (what fits beside the scratch without asking for more shared memory)
+  const size_t smem = 36 * sizeof(float) + (a.keep ? rows : 0);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == FTK_F32) FTK_LAUNCH(norm_mean_kernel<float>, n_tokens, kHyperThreads, 0, s, a);
-  else FTK_LAUNCH(norm_mean_kernel<__nv_bfloat16>, n_tokens, kHyperThreads, 0, s, a);
+  if (dtype == FTK_F32) FTK_LAUNCH(norm_mean_kernel<float>, n_tokens, kHyperThreads, smem, s, a);
+  else FTK_LAUNCH(norm_mean_kernel<__nv_bfloat16>, n_tokens, kHyperThreads, smem, s, a);
   FTK_LAUNCH_CHECK("norm_mean");
   return 0;
 }

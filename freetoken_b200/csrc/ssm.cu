@@ -13,7 +13,7 @@
 
 namespace ftk {
 
-constexpr int kCaTile = 16;      // tokens per tile (at least taps - 1)
+constexpr int kCaTile = 32;      // tokens per tile (at least taps - 1)
 constexpr int kCaMaxTaps = 16;
 constexpr int kCaThreads = 128;  // four channels a thread
 
@@ -28,24 +28,12 @@ conv_act_kernel(const T* __restrict__ x, long long x_stride, const float* __rest
                 int vec_ok) {
   pdl_wait();
   pdl_trigger();
-  int tile = blockIdx.x, seg = 0, q_start = 0, q_len = 0, kv_len = 0;
-  for (; seg < n_segs; ++seg) {
-    q_start = seg_info[seg * 4]; q_len = seg_info[seg * 4 + 1]; kv_len = seg_info[seg * 4 + 2];
-    const int n = q_len > 0 ? (q_len + kCaTile - 1) / kCaTile : 0;
-    if (tile < n) break;
-    tile -= n;
-  }
-  if (seg >= n_segs || q_start < 0 || q_start + q_len > n_tokens || kv_len < q_len) return;
   const int c0 = (blockIdx.y * kCaThreads + threadIdx.x) * 4;
   if (c0 >= C) return;
   const int nc = min(4, C - c0);
   const bool vec = vec_ok && nc == 4;
   if (TAPS > 0) taps = TAPS;
-  const int keep = taps - 1;
-  const int slot = state_slots[seg];
-  const bool has_slot = state && slot >= 0 && slot < n_slots;
-  const int before = kv_len - q_len;
-  float* st = has_slot ? state + ((size_t)slot * keep) * C + c0 : nullptr;  // row r: the input `keep - r` places back
+  // the thread's taps and bias first: they wait for nothing, and the search for the block's request runs beside them
   constexpr int kMost = TAPS > 0 ? TAPS : kCaMaxTaps;
   float wt[kMost][4], bs[4];
 #pragma unroll
@@ -54,6 +42,19 @@ conv_act_kernel(const T* __restrict__ x, long long x_stride, const float* __rest
     for (int i = 0; i < 4; ++i) wt[j][i] = i < nc ? w[(size_t)(c0 + i) * taps + j] : 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) bs[i] = (bias && i < nc) ? bias[c0 + i] : 0.f;
+  int tile = blockIdx.x, seg = 0, q_start = 0, q_len = 0, kv_len = 0;
+  for (; seg < n_segs; ++seg) {
+    q_start = seg_info[seg * 4]; q_len = seg_info[seg * 4 + 1]; kv_len = seg_info[seg * 4 + 2];
+    const int n = q_len > 0 ? (q_len + kCaTile - 1) / kCaTile : 0;
+    if (tile < n) break;
+    tile -= n;
+  }
+  if (seg >= n_segs || q_start < 0 || q_start + q_len > n_tokens || kv_len < q_len) return;
+  const int keep = taps - 1;
+  const int slot = state_slots[seg];
+  const bool has_slot = state && slot >= 0 && slot < n_slots;
+  const int before = kv_len - q_len;
+  float* st = has_slot ? state + ((size_t)slot * keep) * C + c0 : nullptr;  // row r: the input `keep - r` places back
   const bool first = tile == 0;
   const int t0 = tile * kCaTile, t1 = min(q_len, t0 + kCaTile);
   // input `s` places into the request's tokens of this step (negative: before them)
@@ -84,7 +85,8 @@ conv_act_kernel(const T* __restrict__ x, long long x_stride, const float* __rest
       }
     }
   }
-  for (int t = t0; t < t1; ++t) {
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t) {  // (unrolled: several rows' loads are then in flight per thread)
     float cur[4], acc[4];
     input(t, cur);
 #pragma unroll
