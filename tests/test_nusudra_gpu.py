@@ -434,6 +434,63 @@ def test_long_steps_of_latent_rows_of_128_run_the_tensor_core_attention(tmp_path
     eng.check_kernels()
 
 
+REAL_LAYERS = {  # layers of the size of a real model's (no test of the tiny configurations reaches these kernel forms)
+    "architecture": "Nusudra", "vocab": 8192, "width": 2048, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "streams": 4,
+    "layers": [
+        {"type": "parallel", "mixer": {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5},
+                                       "right": {"heads": 32, "vdim": 64, "state": 128, "groups": 4, "conv": 4, "norm_groups": 4}},
+         "mlp": {"kind": "dense", "ff": 4096}},
+        {"type": "delta", "mixer": {"heads": 48, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}, "mlp": {"kind": "dense", "ff": 4096}},
+        {"type": "latent_attention", "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 64, "scale": 192 ** -0.5,
+                                               "rot": {"dims": 64, "base": 1000000.0}}, "mlp": None},
+    ]}
+
+
+def test_layers_of_real_sizes_agree_across_cuts_and_dtypes():
+    """Heads of 128, thousands of state columns, long portions: the pair's attention with bias and sink and the latent
+    attention on the tcgen05 kernels, the delta rule in its form for many columns, the recurrences' chunks side by side.
+    No plain model at these sizes: the 32-bit engine is compared with itself across cuts, the bfloat16 engine with it."""
+    from freetoken_b200.config.engine_config import EngineConfig
+    from freetoken_b200.engine.engine import Engine
+    from test_pabavik_gpu import row_error
+
+    toks = tokens_for(REAL_LAYERS["vocab"], 600, 4)
+    seen = sorted(set(range(0, 600, 7)) | set(range(560, 600)))
+
+    def rows(eng, rid, cuts):
+        got, i, cuts = {}, 0, list(cuts)
+        while i < len(toks):
+            c = min(cuts.pop(0) if cuts else 1, len(toks) - i)
+            want = [p - i for p in seen if i <= p < i + c]
+            out = eng.step([StepEntry(rid, toks[i:i + c], want)])
+            for j, w in enumerate(want):
+                got[w + i] = out.logits[j].float().cpu().clone()
+            i += c
+        eng.close(rid)
+        return torch.stack([got[p] for p in seen])
+
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(EngineConfig(model_path="", dtype=dtype, use_dummy_weight=True, seed=3, page_size=16, max_running_req=4,
+                                  num_page_override=100, max_seq_len_override=1024, max_extend_tokens=640, max_step_tokens=640,
+                                  check_cache=True), raw_config=REAL_LAYERS)
+        ops.variant_counts(reset=True)
+        res[dtype, "whole"] = rows(eng, "w", [600])
+        if dtype == "bfloat16":
+            forms = ops.variant_counts()
+            assert forms.get("attention: tcgen05, 128-row query tiles, bias by distance", 0) == 1, forms
+            assert forms.get("attention: tcgen05, 128-row query tiles", 0) >= 1, forms
+        res[dtype, "cuts"] = rows(eng, "c", [300, 256, 2, 7])
+        eng.check_kernels()
+        del eng
+        torch.cuda.empty_cache()
+    assert torch.isfinite(res["float32", "whole"]).all()
+    assert float(row_error(res["float32", "cuts"], res["float32", "whole"]).max()) < 1e-4
+    assert float(row_error(res["bfloat16", "whole"], res["float32", "whole"]).max()) < 0.08
+    assert float(row_error(res["bfloat16", "cuts"], res["float32", "whole"]).max()) < 0.08
+    assert float(row_error(res["bfloat16", "whole"], res["float32", "whole"]).median()) < 0.03
+
+
 def test_greedy_generation_through_the_scheduler(tmp_path_factory):
     from freetoken_b200 import LLM, SamplingParams
 
