@@ -29,6 +29,10 @@ stream_add_norm        no counterpart: several addends into the 32-bit stream an
                        row statistics (Dynamic Tanh) in one pass
 head_gate, table_route, scale  no counterpart: per-head output gate, experts by a table over
                        token ids, logit scale
+hyper_step, norm_mean  no counterpart: several residual streams (write, read, norm in one pass), the
+                       mean of normed branch outputs
+conv_act, ssm_gates,   no counterpart: convolution of projected rows with a per-request state, step sizes
+ssm_output, delta_scan and decays, gated group norm of a state-space layer; the gated delta rule
 =====================  ==========================================================
 
 ``paged_attention`` runs one of five kernels by ``tile_rows``: 16 (float32, or bfloat16 steps of single
