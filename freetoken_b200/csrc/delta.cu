@@ -12,6 +12,9 @@
 // shuffle rounds, interleaved), and the token's output follows without a second pass: with r = S^T k, p = S^T q of
 // the state before the decay,
 //   u = beta (v - g r),   o = g p + (k . q) u,   S <- g S + k u^T.
+// Tokens go in pairs: the sums over the state for both come from the state as the first finds it, in one pass and one
+// set of shuffle rounds, and the second token's follow from them with the dots k_a . k_b and k_a . q_b; that halves the
+// chain of sums, shuffles and updates that a token cannot start before the one before has ended.
 // The tokens' q, k, v come through shared memory 16 tokens at a time: rows that allow 16-byte copies are fetched a
 // batch ahead with cp.async as they lie in memory while the current batch runs, and a pass from shared to shared
 // memory widens them, makes q and k unit vectors (eight lanes a token) and takes k . q; every slice's channels are
@@ -50,7 +53,7 @@ template <int LPC>
 __host__ __device__ constexpr int delta_cols() { return kDeltaThreads / LPC; }  // value columns per block
 template <typename T, int DPT, int LPC>
 __host__ __device__ constexpr size_t delta_smem_bytes() {
-  return ((size_t)2 * kDeltaBatch * delta_row_len<DPT, LPC>() + kDeltaBatch * delta_cols<LPC>() + 3 * kDeltaBatch) * sizeof(float) +
+  return ((size_t)2 * kDeltaBatch * delta_row_len<DPT, LPC>() + kDeltaBatch * delta_cols<LPC>() + 4 * kDeltaBatch) * sizeof(float) +
          ((size_t)2 * kDeltaBatch * (DPT * LPC + 16 / sizeof(T)) + kDeltaBatch * delta_cols<LPC>()) * sizeof(T);
 }
 
@@ -73,7 +76,9 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
   float* sbeta = sv + kDeltaBatch * kDeltaCols;     // [batch]
   float* sg = sbeta + kDeltaBatch;
   float* skq = sg + kDeltaBatch;
-  T* qraw = reinterpret_cast<T*>(skq + kDeltaBatch);  // [batch][RAWL]: the next batch as it lies in memory
+  float* skk = skq + kDeltaBatch;                   // [batch / 2]: k_a . k_b of the pair of tokens (2j, 2j + 1)
+  float* skq2 = skk + kDeltaBatch / 2;              // [batch / 2]: k_a . q_b
+  T* qraw = reinterpret_cast<T*>(skq2 + kDeltaBatch / 2);  // [batch][RAWL]: the next batch as it lies in memory
   T* kraw = qraw + kDeltaBatch * RAWL;
   T* vraw = kraw + kDeltaBatch * RAWL;              // [batch][cols]
   const int seg = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
@@ -165,18 +170,25 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
     // widen; unit vectors and k . q: eight lanes a token, a warp four tokens at a time
     for (int t = warp * 4 + (lane >> 3); t < kDeltaBatch; t += kDeltaThreads / 8) {
       const int sub = lane & 7;
-      float s2q = 0.f, s2k = 0.f, dkq = 0.f;
+      float s2q = 0.f, s2k = 0.f, dkq = 0.f, dkk = 0.f, dkq2 = 0.f;
+      const int tp = t > 0 ? t - 1 : 0;  // the token before (its dots are used by the odd tokens of a pair)
       for (int d = sub; d < Dp; d += 8) {
         const float qv = to_float(qraw[t * RAWL + d]), kv = to_float(kraw[t * RAWL + d]);
+        const float kp = to_float(kraw[tp * RAWL + d]);
         s2q = fmaf(qv, qv, s2q); s2k = fmaf(kv, kv, s2k); dkq = fmaf(qv, kv, dkq);
+        dkk = fmaf(kp, kv, dkk); dkq2 = fmaf(kp, qv, dkq2);
       }
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) {
         s2q += __shfl_xor_sync(0xffffffffu, s2q, o);
         s2k += __shfl_xor_sync(0xffffffffu, s2k, o);
         dkq += __shfl_xor_sync(0xffffffffu, dkq, o);
+        dkk += __shfl_xor_sync(0xffffffffu, dkk, o);
+        dkq2 += __shfl_xor_sync(0xffffffffu, dkq2, o);
       }
       const float rq = rsqrtf(s2q + a.unit_eps) * a.q_scale, rk = rsqrtf(s2k + a.unit_eps);
+      const float rk_before = __shfl_up_sync(0xffffffffu, rk, 8);  // (an odd token's partner lies eight lanes down)
+      if (sub == 0 && (t & 1)) { skk[t >> 1] = dkk * rk_before * rk; skq2[t >> 1] = dkq2 * rk_before * rq; }
       for (int d = sub; d < Dp; d += 8) {
         const int at = t * RL + d + 4 * (d / DPT);
         sq[at] = to_float(qraw[t * RAWL + d]) * rq;
@@ -190,8 +202,58 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(DeltaArgs a) 
       if (wide) fetch(b0 + kDeltaBatch);
       fetch_gates(b0 + kDeltaBatch);
     }
-#pragma unroll 4
-    for (int t = 0; t < nb; ++t) {
+    // two tokens at a time: S^T k and S^T q of both from the state as the first finds it (one pass, one set of shuffle
+    // rounds); with the pair's dots k_a . k_b and k_a . q_b the second token's sums over the state the first leaves follow:
+    //   S_a^T k_b = g_a S^T k_b + (k_a . k_b) u_a,   S_a^T q_b = g_a S^T q_b + (k_a . q_b) u_a
+    int t_done = 0;
+#pragma unroll 2
+    for (int t = 0; t + 1 < nb; t += 2) {
+      const float ga = sg[t], gb = sg[t + 1], ba = sbeta[t], bb2 = sbeta[t + 1], kqa = skq[t], kqb = skq[t + 1];
+      const float kk = skk[t >> 1], kqab = skq2[t >> 1];
+      const float va = sv[t * kDeltaCols + lcol], vb2 = sv[(t + 1) * kDeltaCols + lcol];
+      const float4* ka4 = reinterpret_cast<const float4*>(sk + t * RL + d0 + 4 * slice);
+      const float4* qa4 = reinterpret_cast<const float4*>(sq + t * RL + d0 + 4 * slice);
+      const float4* kb4 = reinterpret_cast<const float4*>(sk + (t + 1) * RL + d0 + 4 * slice);
+      const float4* qb4 = reinterpret_cast<const float4*>(sq + (t + 1) * RL + d0 + 4 * slice);
+      float ra[2] = {0.f, 0.f}, pa[2] = {0.f, 0.f}, rb[2] = {0.f, 0.f}, pb[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < DPT / 4; ++i) {
+        const float4 ka = ka4[i], qa = qa4[i], kb = kb4[i], qb = qb4[i];
+        ra[0] = fmaf(s[4 * i + 0], ka.x, ra[0]); pa[0] = fmaf(s[4 * i + 0], qa.x, pa[0]);
+        rb[0] = fmaf(s[4 * i + 0], kb.x, rb[0]); pb[0] = fmaf(s[4 * i + 0], qb.x, pb[0]);
+        ra[1] = fmaf(s[4 * i + 1], ka.y, ra[1]); pa[1] = fmaf(s[4 * i + 1], qa.y, pa[1]);
+        rb[1] = fmaf(s[4 * i + 1], kb.y, rb[1]); pb[1] = fmaf(s[4 * i + 1], qb.y, pb[1]);
+        ra[0] = fmaf(s[4 * i + 2], ka.z, ra[0]); pa[0] = fmaf(s[4 * i + 2], qa.z, pa[0]);
+        rb[0] = fmaf(s[4 * i + 2], kb.z, rb[0]); pb[0] = fmaf(s[4 * i + 2], qb.z, pb[0]);
+        ra[1] = fmaf(s[4 * i + 3], ka.w, ra[1]); pa[1] = fmaf(s[4 * i + 3], qa.w, pa[1]);
+        rb[1] = fmaf(s[4 * i + 3], kb.w, rb[1]); pb[1] = fmaf(s[4 * i + 3], qb.w, pb[1]);
+      }
+      float ras = ra[0] + ra[1], pas = pa[0] + pa[1], rbs = rb[0] + rb[1], pbs = pb[0] + pb[1];
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) {
+        ras += __shfl_xor_sync(0xffffffffu, ras, o);
+        rbs += __shfl_xor_sync(0xffffffffu, rbs, o);
+        pas += __shfl_xor_sync(0xffffffffu, pas, o);
+        pbs += __shfl_xor_sync(0xffffffffu, pbs, o);
+      }
+      const float ua = ba * (va - ga * ras);
+      const float ub = bb2 * (vb2 - gb * fmaf(ga, rbs, kk * ua));
+      const float gab = ga * gb, wa = gb * ua;
+#pragma unroll
+      for (int i = 0; i < DPT / 4; ++i) {  // S <- g_b (g_a S + k_a u_a^T) + k_b u_b^T
+        const float4 ka = ka4[i], kb = kb4[i];
+        s[4 * i + 0] = fmaf(gab, s[4 * i + 0], fmaf(wa, ka.x, ub * kb.x));
+        s[4 * i + 1] = fmaf(gab, s[4 * i + 1], fmaf(wa, ka.y, ub * kb.y));
+        s[4 * i + 2] = fmaf(gab, s[4 * i + 2], fmaf(wa, ka.z, ub * kb.z));
+        s[4 * i + 3] = fmaf(gab, s[4 * i + 3], fmaf(wa, ka.w, ub * kb.w));
+      }
+      if (slice == 0) {
+        so[t * kDeltaCols + lcol] = fmaf(ga, pas, kqa * ua);
+        so[(t + 1) * kDeltaCols + lcol] = fmaf(gb, fmaf(ga, pbs, kqab * ua), kqb * ub);
+      }
+      t_done = t + 2;
+    }
+    for (int t = t_done; t < nb; ++t) {  // (a batch's odd last token)
       const float g = sg[t], beta = sbeta[t], kq = skq[t], vj = sv[t * kDeltaCols + lcol];
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * RL + d0 + 4 * slice);
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * RL + d0 + 4 * slice);
